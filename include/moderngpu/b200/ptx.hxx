@@ -1,0 +1,118 @@
+// Thin wrappers over the sm_100a instructions the kernels use directly:
+// shared-memory transaction barriers (mbarrier), bulk asynchronous copies
+// from global to this CTA's shared memory (the TMA engine's untiled form,
+// always to the issuing CTA only), named barriers for a subset of a CTA,
+// and scoped loads/stores for the cross-CTA tile-status protocol.
+//
+// Every wait is bounded: it returns false after `spin_limit` polls so the
+// caller can record a status and leave instead of spinning forever.
+#pragma once
+#include "base.hxx"
+
+#ifdef __CUDACC__
+
+BEGIN_MGPU_NAMESPACE
+namespace ptx {
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// mbarrier
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;"
+    :: "r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+
+// Makes barrier initialisation and earlier generic-proxy shared-memory
+// accesses visible to the asynchronous (bulk copy) proxy.
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];"
+    :: "r"(smem_addr(bar)) : "memory");
+}
+
+// One arrival that also announces `bytes` of bulk-copy traffic to wait for.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar,
+  uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+    :: "r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+    "{\n"
+    "  .reg .pred p;\n"
+    "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+    "  selp.u32 %0, 1, 0, p;\n"
+    "}\n"
+    : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+
+// Bounded wait for the phase with the given parity to complete.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+  uint32_t spin_limit) {
+  for(uint32_t spin = 0; spin < spin_limit; ++spin) {
+    if(mbar_try_wait(bar, parity)) return true;
+    if(spin > 64) __nanosleep(64);
+  }
+  return false;
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// Bulk copy global -> shared memory of the issuing CTA, completion counted
+// in bytes on an mbarrier. Source, destination and size must be multiples of
+// 16 bytes.
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src,
+  uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes "
+    "[%0], [%1], %2, [%3];"
+    :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes),
+       "r"(smem_addr(bar)) : "memory");
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// Named barrier over `count` threads (a multiple of 32) of the CTA.
+
+template<int id, int count>
+__device__ __forceinline__ void named_sync() {
+  asm volatile("bar.sync %0, %1;" :: "n"(id), "n"(count) : "memory");
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// Device-scope loads and stores for flags shared between CTAs.
+
+__device__ __forceinline__ uint64_t ld_relaxed_u64(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p)
+    : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_relaxed_u64(uint64_t* p, uint64_t v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v)
+    : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p)
+    : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v)
+    : "memory");
+}
+
+} // namespace ptx
+END_MGPU_NAMESPACE
+
+#endif // __CUDACC__

@@ -1,0 +1,629 @@
+// Single-pass load-balanced segmented reduction for sm_100a.
+//
+// Replaces the reference's tile kernel plus recursive fix-up
+// (src/moderngpu/kernel_segreduce.hxx:17-100 cta_segreduce_t, :105-185
+// segreduce_fixup, :219-263 k_reduce) and its CTA segmented scan
+// (src/moderngpu/cta_segscan.hxx:16-104) with one persistent kernel.
+//
+// Work decomposition. Items and segment starts are merged (a start sorts
+// before the item with the same index) and cut into tiles of `nv` merged
+// elements by the partitioner, so a tile never holds more than nv items nor
+// more than nv segment starts. Tile t owns items [a0, a1) and segment starts
+// [b0, b1). The tile that holds the START of segment j is the one that writes
+// output[j-1]: every item of segment j-1 lies in that tile or in earlier
+// ones. The last tile also writes the last segment.
+//
+// A CTA is nt consumer threads plus one producer warp.
+//  * Producer (one lane): takes the next tile from a global ticket counter,
+//    reads its two partition values, and issues bulk asynchronous copies of
+//    the tile's item window and segment-start window from HBM into one of
+//    `stages` shared-memory buffers, completion counted on an mbarrier.
+//    Several tiles are in flight per CTA at any time.
+//  * Consumers, per tile:
+//      1. scatter a head-flag bit for every segment start of the tile into a
+//         shared bitmask; write `init` for empty segments;
+//      2. each thread folds vt consecutive items taken from shared memory
+//         with 128-bit loads, restarting at head flags;
+//      3. warp-shuffle segmented scan of the per-thread partials, one
+//         shared-memory hop across warps;
+//      4. second sweep over the registers: values at segment ends are stored
+//         in place; a second pass over the segment starts copies them to
+//         output[] (coalesced);
+//      5. the value of the segment open at the tile's right edge is published
+//         in the tile-status array; the one output that needs items of
+//         earlier tiles is finished by a warp that looks back through that
+//         array (tile_state.hxx).
+//
+// Results: each segment is folded strictly left to right within a thread and
+// combined as op(earlier, later) everywhere else; `init` is written for empty
+// segments and never folded into a non-empty one (reference behaviour,
+// tests/test_segreduce.cu:40-49). Integer results are exact; floating-point
+// sums differ from a serial sum only by association.
+#pragma once
+#include "partition.hxx"
+#include "tile_state.hxx"
+
+#ifdef __CUDACC__
+
+BEGIN_MGPU_NAMESPACE
+
+// Tile shape: nt consumer threads x vt items per thread, `stages` buffers per
+// CTA, at least `occ` CTAs per SM.
+template<int nt_, int vt_, int stages_, int occ_>
+struct segreduce_tuning_t {
+  enum { nt = nt_, vt = vt_, stages = stages_, occ = occ_,
+    nv = nt_ * vt_ - 8 };
+  static_assert(nt_ % 32 == 0 && vt_ >= 4 && vt_ <= 31, "unsupported tile");
+};
+
+namespace detail {
+
+// Blackwell defaults, chosen from measurements on B200: vt is picked so that
+// a thread's run of vt values starts on a 16-byte boundary and the 128-bit
+// shared-memory loads of a quarter warp hit distinct banks.
+template<typename type_t, int size = (int)sizeof(type_t)>
+struct segreduce_default_tuning { typedef segreduce_tuning_t<128, 4, 2, 4> type; };
+template<typename type_t>
+struct segreduce_default_tuning<type_t, 1> { typedef segreduce_tuning_t<256, 16, 3, 3> type; };
+template<typename type_t>
+struct segreduce_default_tuning<type_t, 2> { typedef segreduce_tuning_t<256, 16, 3, 3> type; };
+template<typename type_t>
+struct segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<256, 20, 3, 3> type; };
+template<typename type_t>
+struct segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 10, 3, 3> type; };
+template<typename type_t>
+struct segreduce_default_tuning<type_t, 16> { typedef segreduce_tuning_t<256, 5, 3, 3> type; };
+
+////////////////////////////////////////////////////////////////////////////////
+// Value sources.
+
+// Contiguous array of type_t in global memory: staged by bulk copies.
+template<typename type_t>
+struct array_source_t {
+  enum { bulk = 1 };
+  const type_t* data;
+  MGPU_DEVICE type_t load(int index) const { return data[index]; }
+};
+
+// Anything with operator[]: evaluated by the consumer threads.
+template<typename input_it, typename type_t>
+struct iterator_source_t {
+  enum { bulk = 0 };
+  input_it input;
+  MGPU_DEVICE type_t load(int index) const { return (type_t)input[index]; }
+};
+
+template<typename input_it, typename type_t>
+struct source_for {
+  typedef typename std::iterator_traits<input_it>::value_type value_t;
+  enum { bulk = std::is_pointer<input_it>::value &&
+    std::is_same<typename std::remove_cv<value_t>::type, type_t>::value &&
+    std::is_arithmetic<type_t>::value &&
+    (sizeof(type_t) == 4 || sizeof(type_t) == 8) };
+  typedef typename std::conditional<bulk, array_source_t<type_t>,
+    iterator_source_t<input_it, type_t> >::type type;
+};
+
+template<typename segments_it>
+struct segments_are_int_array {
+  typedef typename std::iterator_traits<segments_it>::value_type value_t;
+  enum { value = std::is_pointer<segments_it>::value &&
+    std::is_same<typename std::remove_cv<value_t>::type, int>::value };
+};
+
+////////////////////////////////////////////////////////////////////////////////
+
+// What the producer tells the consumers about a staged tile. Positions
+// ("w") index the stage buffer's value array; item a0 sits at w == lo.
+struct tile_desc_t {
+  int tile;             // -1: no more tiles
+  int a0, a1, b0, b1;   // items [a0, a1), segment starts [b0, b1)
+  int lo;               // position of item a0
+  int src_lo, src_hi;   // positions delivered by the bulk copy
+  int ob, oe;           // segment indices whose offsets are staged
+  int offs_byte;        // byte offset of the staged offsets in the stage
+  int pad;
+};
+
+template<typename type_t, typename source_t, typename segments_it,
+  typename output_it, typename op_t>
+struct segreduce_args_t {
+  source_t source;
+  segments_it segments;
+  output_it output;
+  op_t op;
+  type_t init;
+  int count, num_segments, num_tiles;
+  const int* partitions;
+  uint32_t* header;       // [0] ticket counter, [1] status
+  void* tile_state;
+  uint32_t spin_limit;
+};
+
+template<typename tuning_t, typename type_t>
+struct segreduce_smem_t {
+  enum {
+    nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
+    nv = tuning_t::nv, warps = nt / 32,
+    flag_words = nt * vt / 32 + 2,
+    elem = (int)sizeof(type_t),
+    wide = elem > 4 ? elem : 4,
+    stage_bytes = (nv * wide + 8 * elem + 64 + 127) / 128 * 128
+  };
+  struct fixed_t {
+    uint64_t full[stages];
+    uint64_t empty[stages];
+    tile_desc_t desc[stages];
+    uint32_t flags[2][flag_words];
+    int warp_head[warps];
+    alignas(16) char warp_agg[warps * elem];
+  };
+  enum {
+    fixed_bytes = ((int)sizeof(fixed_t) + 127) / 128 * 128,
+    total_bytes = fixed_bytes + stages * stage_bytes
+  };
+};
+
+// vt consecutive values from shared memory into registers.
+template<int vt, typename type_t>
+MGPU_DEVICE void load_chunk(const type_t* src, type_t (&v)[vt]) {
+  if constexpr ((vt * sizeof(type_t)) % 16 == 0 &&
+    std::is_trivially_copyable<type_t>::value) {
+    enum { quads = vt * sizeof(type_t) / 16 };
+    uint4 q[quads];
+    const uint4* p = reinterpret_cast<const uint4*>(src);
+    #pragma unroll
+    for(int i = 0; i < quads; ++i) q[i] = p[i];
+    memcpy(v, q, sizeof(q));
+  } else {
+    #pragma unroll
+    for(int i = 0; i < vt; ++i) v[i] = src[i];
+  }
+}
+
+template<typename tuning_t, typename type_t, typename source_t,
+  typename segments_it, typename output_it, typename op_t>
+__global__ void __launch_bounds__(tuning_t::nt + 32, tuning_t::occ)
+segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
+  op_t> args) {
+
+  typedef segreduce_smem_t<tuning_t, type_t> layout_t;
+  typedef typename layout_t::fixed_t fixed_t;
+  enum { nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
+    nv = tuning_t::nv, warps = nt / 32, flag_words = layout_t::flag_words,
+    elem = layout_t::elem, stage_bytes = layout_t::stage_bytes,
+    src_bulk = source_t::bulk,
+    seg_bulk = segments_are_int_array<segments_it>::value };
+
+  extern __shared__ __align__(128) char smem_raw[];
+  fixed_t& fixed = *reinterpret_cast<fixed_t*>(smem_raw);
+  char* stage_base = smem_raw + layout_t::fixed_bytes;
+
+  const int tid = (int)threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int count = args.count;
+  const int num_segments = args.num_segments;
+  const int num_tiles = args.num_tiles;
+
+  if(0 == tid) {
+    for(int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&fixed.full[s], 1);
+      ptx::mbar_init(&fixed.empty[s], nt);
+      fixed.desc[s].tile = -1;
+    }
+    ptx::fence_proxy_async();
+  }
+  for(int i = tid; i < 2 * flag_words; i += nt + 32)
+    (&fixed.flags[0][0])[i] = 0;
+  __syncthreads();
+
+  //////////////////////////////////////////////////////////////////////////////
+  // Producer warp.
+
+  if(warp == warps) {
+    if(lane) return;
+    const int64_t total = (int64_t)count + num_segments;
+    for(int it = 0; ; ++it) {
+      int s = it % stages;
+      int use = it / stages;
+      if(use > 0 &&
+        !ptx::mbar_wait(&fixed.empty[s], (use - 1) & 1, args.spin_limit))
+        atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+
+      tile_desc_t d;
+      d.tile = (int)atomicAdd(args.header, 1u);
+      if(d.tile >= num_tiles) {
+        fixed.desc[s].tile = -1;
+        ptx::mbar_arrive(&fixed.full[s]);
+        break;
+      }
+      d.a0 = args.partitions[d.tile];
+      d.a1 = args.partitions[d.tile + 1];
+      int64_t d0 = (int64_t)d.tile * nv;
+      int64_t d1 = d0 + nv < total ? d0 + nv : total;
+      d.b0 = (int)(d0 - d.a0);
+      d.b1 = (int)(d1 - d.a1);
+      d.pad = 0;
+      char* stage = stage_base + s * stage_bytes;
+      int na = d.a1 - d.a0;
+
+      // Item window: whole 16-byte granules of the input array.
+      uint32_t item_bytes = 0;
+      const char* item_src = nullptr;
+      char* item_dst = nullptr;
+      int items_end;
+      if constexpr (src_bulk) {
+        enum { per16 = 16 / elem };
+        const type_t* data = args.source.data;
+        int mis = (int)(((uintptr_t)data / elem) % per16);
+        int64_t u0 = (int64_t)d.a0 + mis;
+        int64_t ubase = u0 / per16 * per16;
+        d.lo = (int)(u0 - ubase);
+        int64_t inner_lo = mis ? per16 : 0;
+        int64_t inner_hi = ((int64_t)count + mis) / per16 * per16;
+        int64_t c_lo = ubase > inner_lo ? ubase : inner_lo;
+        int64_t c_hi = ((int64_t)d.a1 + mis + per16 - 1) / per16 * per16;
+        if(c_hi > inner_hi) c_hi = inner_hi;
+        d.src_lo = d.src_hi = 0;
+        if(na > 0 && c_hi > c_lo) {
+          item_bytes = (uint32_t)((c_hi - c_lo) * elem);
+          item_src = (const char*)(data + (c_lo - mis));
+          item_dst = stage + (c_lo - ubase) * elem;
+          d.src_lo = (int)(c_lo - ubase);
+          d.src_hi = (int)(c_hi - ubase);
+        }
+        items_end = (d.lo + na + per16 - 1) / per16 * per16;
+      } else {
+        d.lo = 0;
+        d.src_lo = 0;
+        d.src_hi = na;
+        items_end = na;
+      }
+      d.offs_byte = (items_end * elem + 15) / 16 * 16;
+
+      // Segment-start window [b0 - 1, b1), again whole granules.
+      int jlo = d.b0 > 0 ? d.b0 - 1 : 0;
+      int jhi = d.b1;
+      uint32_t offs_bytes = 0;
+      const char* offs_src = nullptr;
+      if constexpr (seg_bulk) {
+        const int* seg = args.segments;
+        int mis = (int)(((uintptr_t)seg / 4) % 4);
+        int64_t inner_lo = mis ? 4 : 0;
+        int64_t inner_hi = ((int64_t)num_segments + mis) / 4 * 4;
+        int64_t c_lo = ((int64_t)jlo + mis) / 4 * 4;
+        if(c_lo < inner_lo) c_lo = inner_lo;
+        int64_t c_hi = ((int64_t)jhi + mis + 3) / 4 * 4;
+        if(c_hi > inner_hi) c_hi = inner_hi;
+        d.ob = d.oe = 0;
+        if(jhi > jlo && c_hi > c_lo) {
+          offs_bytes = (uint32_t)((c_hi - c_lo) * 4);
+          offs_src = (const char*)(seg + (c_lo - mis));
+          d.ob = (int)(c_lo - mis);
+          d.oe = (int)(c_hi - mis);
+        }
+      } else {
+        d.ob = jlo;
+        d.oe = jhi;
+      }
+
+      fixed.desc[s] = d;
+      if(item_bytes + offs_bytes) {
+        ptx::mbar_arrive_expect_tx(&fixed.full[s], item_bytes + offs_bytes);
+        if(item_bytes)
+          ptx::bulk_load(item_dst, item_src, item_bytes, &fixed.full[s]);
+        if(offs_bytes)
+          ptx::bulk_load(stage + d.offs_byte, offs_src, offs_bytes,
+            &fixed.full[s]);
+      } else {
+        ptx::mbar_arrive(&fixed.full[s]);
+      }
+    }
+    return;
+  }
+
+  //////////////////////////////////////////////////////////////////////////////
+  // Consumers.
+
+  op_t op = args.op;
+  const type_t init = args.init;
+  tile_state_t<type_t> state;
+  state.bind(args.tile_state, num_tiles);
+  type_t* warp_agg = reinterpret_cast<type_t*>(fixed.warp_agg);
+  const unsigned full_mask = 0xffffffffu;
+  const uint32_t vt_mask = (1u << vt) - 1;
+
+  for(int it = 0; ; ++it) {
+    int s = it % stages;
+    if(!ptx::mbar_wait(&fixed.full[s], (it / stages) & 1, args.spin_limit))
+      atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+    const tile_desc_t d = fixed.desc[s];
+    if(d.tile < 0) break;
+
+    char* stage = stage_base + s * stage_bytes;
+    type_t* vals = reinterpret_cast<type_t*>(stage);
+    int* offs = reinterpret_cast<int*>(stage + d.offs_byte);
+    uint32_t* flags = fixed.flags[it & 1];
+    uint32_t* flags_next = fixed.flags[(it + 1) & 1];
+
+    const int a0 = d.a0, a1 = d.a1, b0 = d.b0, b1 = d.b1, lo = d.lo;
+    const int na = a1 - a0;
+    const int nb = b1 - b0;
+    const int hi = lo + na;
+    const bool is_last = d.tile == num_tiles - 1;
+    const int jend = b1 + (is_last ? 1 : 0);
+    const int ob = d.ob, oe = d.oe;
+
+    // Start offset of segment j; j == num_segments is the end of the array.
+    auto seg_start = [&](int j) -> int {
+      if(j >= num_segments) return count;
+      if(j >= ob && j < oe) return offs[j - ob];
+      return (int)args.segments[j];
+    };
+
+    if constexpr (!src_bulk) {
+      for(int i = tid; i < na; i += nt) vals[i] = args.source.load(a0 + i);
+    }
+    if constexpr (!seg_bulk) {
+      for(int j = ob + tid; j < oe; j += nt)
+        offs[j - ob] = (int)args.segments[j];
+      ptx::named_sync<1, nt>();
+    }
+
+    // 1. Head flags, and `init` for empty segments.
+    for(int j = b0 + tid; j < jend; j += nt) {
+      int p = seg_start(j);
+      if(j < b1) {
+        int rel = p - a0;
+        rel = rel < 0 ? 0 : (rel > na ? na : rel);
+        int w = lo + rel;
+        atomicOr(&flags[w >> 5], 1u << (w & 31));
+      }
+      if(j > 0 && seg_start(j - 1) == p) args.output[j - 1] = init;
+    }
+    if(0 == tid) {
+      atomicOr(&flags[hi >> 5], 1u << (hi & 31));
+      if(0 == na) state.publish(d.tile, tile_closed);
+    }
+    ptx::named_sync<1, nt>();
+
+    if(na > 0) {
+      // 2. Per-thread fold of positions [w0, w0 + vt).
+      const int w0 = tid * vt;
+      const bool fast = w0 >= lo && w0 + vt <= hi &&
+        w0 >= d.src_lo && w0 + vt <= d.src_hi;
+      int i_lo = lo > w0 ? lo - w0 : 0;
+      int i_hi = hi - w0 < vt ? hi - w0 : vt;
+      uint32_t bits = __funnelshift_r(flags[w0 >> 5], flags[(w0 >> 5) + 1],
+        w0 & 31);
+
+      type_t v[vt];
+      type_t x = init;
+      bool head = true;
+      if(fast) {
+        load_chunk<vt>(vals + w0, v);
+        x = v[0];
+        #pragma unroll
+        for(int i = 1; i < vt; ++i)
+          x = ((bits >> i) & 1) ? v[i] : op(x, v[i]);
+        head = 0 != (bits & vt_mask);
+      } else if(i_lo < i_hi) {
+        if constexpr (src_bulk) {
+          // Array elements outside the 16-byte-aligned interior.
+          for(int i = i_lo; i < i_hi; ++i) {
+            int w = w0 + i;
+            if(w < d.src_lo || w >= d.src_hi)
+              vals[w] = args.source.load(a0 + (w - lo));
+          }
+        }
+        x = vals[w0 + i_lo];
+        for(int i = i_lo + 1; i < i_hi; ++i) {
+          type_t y = vals[w0 + i];
+          x = ((bits >> i) & 1) ? y : op(x, y);
+        }
+        uint32_t range = (i_hi >= 32 ? full_mask : ((1u << i_hi) - 1)) &
+          ~((1u << i_lo) - 1);
+        head = 0 != (bits & range);
+      }
+
+      // 3. Segmented scan of (head, x) across the CTA.
+      unsigned head_mask = __ballot_sync(full_mask, head);
+      unsigned at_or_below = head_mask & (full_mask >> (31 - lane));
+      int run_start = at_or_below ? 31 - __clz(at_or_below) : 0;
+      type_t incl = x;
+      #pragma unroll
+      for(int delta = 1; delta < 32; delta *= 2) {
+        type_t y = shfl_up_any(incl, delta);
+        if(lane - delta >= run_start) incl = op(y, incl);
+      }
+      type_t from_left = shfl_up_any(incl, 1);
+      if(31 == lane) {
+        warp_agg[warp] = incl;
+        fixed.warp_head[warp] = 0 != head_mask;
+      }
+      ptx::named_sync<1, nt>();
+
+      bool head_before = 0 != (head_mask & ((1u << lane) - 1));
+      bool has_c = lane > 0;
+      type_t c = from_left;
+      if(!head_before && warp > 0) {
+        // The run reaching this thread began in an earlier warp.
+        type_t cw = warp_agg[warp - 1];
+        for(int k = warp - 1; k > 0 && !fixed.warp_head[k]; --k)
+          cw = op(warp_agg[k - 1], cw);
+        c = has_c ? op(cw, c) : cw;
+        has_c = true;
+      }
+
+      // 4. Values at segment ends, stored in place; the open segment's value
+      // at the right edge goes to the tile-status array.
+      uint32_t ends = bits >> 1;
+      type_t y = init;
+      bool at_edge = false;
+      if(fast) {
+        if(ends & vt_mask) {
+          y = ((bits & 1) || !has_c) ? v[0] : op(c, v[0]);
+          if(ends & 1) vals[w0] = y;
+          #pragma unroll
+          for(int i = 1; i < vt; ++i) {
+            y = ((bits >> i) & 1) ? v[i] : op(y, v[i]);
+            if((ends >> i) & 1) vals[w0 + i] = y;
+          }
+          at_edge = w0 + vt == hi;
+        }
+      } else if(i_lo < i_hi) {
+        type_t first = vals[w0 + i_lo];
+        y = (((bits >> i_lo) & 1) || !has_c) ? first : op(c, first);
+        if((ends >> i_lo) & 1) vals[w0 + i_lo] = y;
+        for(int i = i_lo + 1; i < i_hi; ++i) {
+          type_t z = vals[w0 + i];
+          y = ((bits >> i) & 1) ? z : op(y, z);
+          if((ends >> i) & 1) vals[w0 + i] = y;
+        }
+        at_edge = w0 + i_hi == hi;
+      }
+      if(at_edge) {
+        uint32_t code;
+        if(nb > 0) code = seg_start(b1 - 1) == a1 ? tile_closed :
+          tile_inclusive;
+        else code = d.tile ? tile_partial : tile_inclusive;
+        state.publish(d.tile, code, y);
+      }
+    }
+
+    for(int i = tid; i < flag_words; i += nt) flags_next[i] = 0;
+    ptx::named_sync<1, nt>();
+
+    // 5. Outputs of the segments that end in this tile. The first one may
+    // need items of earlier tiles and is finished by warp 0 below.
+    const bool first_valid = b0 >= 1 && b0 < jend;
+    int prev0 = 0, p0 = 0;
+    bool need_out = false;
+    if(first_valid) {
+      prev0 = seg_start(b0 - 1);
+      p0 = seg_start(b0);
+      need_out = prev0 != p0;
+    }
+    const bool partial_tile = 0 == nb && d.tile > 0;
+    int q0 = p0 - a0;
+    q0 = q0 < 0 ? 0 : (q0 > na ? na : q0);
+    type_t lead = init, tail = init;
+    if(0 == warp) {
+      if(need_out && q0 > 0) lead = vals[lo + q0 - 1];
+      if(partial_tile) tail = vals[hi - 1];
+    }
+    for(int j = b0 + 1 + tid; j < jend; j += nt) {
+      int p = seg_start(j);
+      if(seg_start(j - 1) != p) {
+        int rel = p - a0;
+        rel = rel < 1 ? 1 : (rel > na ? na : rel);
+        args.output[j - 1] = vals[lo + rel - 1];
+      }
+    }
+    ptx::fence_proxy_async();
+    ptx::mbar_arrive(&fixed.empty[s]);
+
+    if(0 == warp) {
+      bool need_carry = need_out && prev0 < a0 && d.tile > 0;
+      bool have = false;
+      type_t carry = init;
+      if(need_carry || partial_tile)
+        have = lookback(state, d.tile, op, carry, args.spin_limit,
+          args.header + 1);
+      if(0 == lane) {
+        if(partial_tile)
+          state.publish(d.tile, tile_inclusive, have ? op(carry, tail) : tail);
+        if(need_out) {
+          type_t r = lead;
+          if(need_carry && have) r = q0 > 0 ? op(carry, lead) : carry;
+          args.output[b0 - 1] = r;
+        }
+      }
+    }
+  }
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// Host side.
+
+// Workspace layout: [header 128 B][partitions][tile status].
+template<typename tuning_t, typename type_t>
+struct segreduce_plan_t {
+  int num_tiles;
+  size_t partitions_offset, state_offset, bytes;
+
+  segreduce_plan_t(int count, int num_segments) {
+    int64_t total = (int64_t)count + num_segments;
+    num_tiles = (int)div_up(total, (int64_t)tuning_t::nv);
+    partitions_offset = 128;
+    size_t part_bytes = ((size_t)(num_tiles + 1) * 4 + 127) / 128 * 128;
+    state_offset = partitions_offset + part_bytes;
+    bytes = state_offset + tile_state_bytes<type_t>(num_tiles) + 128;
+  }
+};
+
+// CTAs of `kernel` that fit on the current device at once. `tag_t` must be
+// unique per kernel instantiation: the answer is cached per (tag, device).
+template<typename tag_t, typename kernel_t>
+int resident_ctas(kernel_t kernel, int threads, int smem_bytes) {
+  int device = 0;
+  throw_on_error(cudaGetDevice(&device));
+  static int cached[64] = { };
+  if(device < 64 && cached[device]) return cached[device];
+  throw_on_error(cudaFuncSetAttribute(kernel,
+    cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+  int per_sm = 0, sms = 0;
+  throw_on_error(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm,
+    kernel, threads, smem_bytes));
+  throw_on_error(cudaDeviceGetAttribute(&sms,
+    cudaDevAttrMultiProcessorCount, device));
+  int n = per_sm * sms;
+  if(n < 1) n = 1;
+  if(device < 64) cached[device] = n;
+  return n;
+}
+
+enum : uint32_t { default_spin_limit = 1u << 24 };
+
+// Enqueue partitioner + reduction on `stream`. `workspace` must hold
+// segreduce_plan_t<...>(count, num_segments).bytes bytes, 128-byte aligned.
+template<typename tuning_t, typename type_t, typename source_t,
+  typename segments_it, typename output_it, typename op_t>
+void segreduce_enqueue(source_t source, int count, segments_it segments,
+  int num_segments, output_it output, op_t op, type_t init, void* workspace,
+  cudaStream_t stream, uint32_t spin_limit = default_spin_limit) {
+
+  typedef segreduce_smem_t<tuning_t, type_t> layout_t;
+  typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t>
+    args_t;
+  segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);
+  if(!plan.num_tiles) return;
+
+  char* base = (char*)workspace;
+  uint32_t* header = (uint32_t*)base;
+  int* partitions = (int*)(base + plan.partitions_offset);
+  void* state = base + plan.state_offset;
+
+  launch_lbs_partition(segments, count, num_segments,
+    (int64_t)tuning_t::nv, plan.num_tiles + 1, partitions, stream,
+    header, 32, (uint32_t*)state,
+    (int)tile_state_traits<type_t>::clear_words);
+
+  auto kernel = segreduce_k<tuning_t, type_t, source_t, segments_it,
+    output_it, op_t>;
+  int threads = tuning_t::nt + 32;
+  int resident = resident_ctas<tuple<tuning_t, args_t> >(kernel, threads,
+    (int)layout_t::total_bytes);
+  int grid = plan.num_tiles < resident ? plan.num_tiles : resident;
+
+  args_t args { source, segments, output, op, init, count, num_segments,
+    plan.num_tiles, partitions, header, state, spin_limit };
+  kernel<<<grid, threads, layout_t::total_bytes, stream>>>(args);
+}
+
+} // namespace detail
+
+END_MGPU_NAMESPACE
+
+#endif // __CUDACC__

@@ -1,0 +1,219 @@
+// Per-tile status words for the single-pass ("decoupled look-back") carry
+// between tiles of a segmented reduction.
+//
+// The reference finishes a segmented reduction with a second, recursive
+// fix-up pass over per-CTA carry-outs (src/moderngpu/kernel_segreduce.hxx:
+// 105-185). Here every tile publishes, as soon as it knows it, the value of
+// the segment still open at its right edge, and a later tile that needs the
+// part of its first segment lying to its left reads those words backwards
+// until it meets a tile whose value no longer depends on anything earlier.
+//
+// A tile's word is one of
+//   tile_empty          nothing published yet
+//   tile_partial        fold of ALL items of the tile; the tile holds no
+//                       segment start, so earlier tiles still contribute
+//   tile_inclusive      fold of the open segment up to the tile's right edge,
+//                       everything to the left already included
+//   tile_closed         a segment start sits exactly on the tile's right
+//                       edge: the open segment has no items yet
+// Readers stop at the first tile_inclusive or tile_closed word.
+#pragma once
+#include "ptx.hxx"
+
+#ifdef __CUDACC__
+
+BEGIN_MGPU_NAMESPACE
+namespace detail {
+
+enum : uint32_t {
+  tile_empty = 0,
+  tile_partial = 1,
+  tile_inclusive = 2,
+  tile_closed = 3
+};
+
+// Status codes reported through the workspace header.
+enum : uint32_t {
+  status_ok = 0,
+  status_lookback_timeout = 1,   // a predecessor tile never published
+  status_copy_timeout = 2        // a staged copy never completed
+};
+
+template<typename type_t>
+struct tile_state_traits {
+  // Value and code travel in one 64-bit word when the value fits in 32 bits;
+  // otherwise the code is released after the value has been written.
+  enum { packed = sizeof(type_t) <= 4 &&
+    std::is_trivially_copyable<type_t>::value };
+  enum { slot_bytes = (sizeof(type_t) + 7) / 8 * 8 };
+  // 32-bit words per tile that must read zero before a launch.
+  enum { clear_words = packed ? 2 : 1 };
+};
+
+// Bytes of tile-status storage for num_tiles tiles.
+template<typename type_t>
+inline size_t tile_state_bytes(int num_tiles) {
+  typedef tile_state_traits<type_t> traits;
+  size_t n = (size_t)num_tiles;
+  if(traits::packed) return n * 8;
+  size_t codes = (n * 4 + 127) / 128 * 128;
+  return codes + 2 * n * traits::slot_bytes;
+}
+
+template<typename type_t, bool packed = tile_state_traits<type_t>::packed>
+struct tile_state_t;
+
+template<typename type_t>
+struct tile_state_t<type_t, true> {
+  uint64_t* words;
+
+  MGPU_DEVICE void bind(void* base, int) { words = (uint64_t*)base; }
+
+  MGPU_DEVICE void publish(int tile, uint32_t code, type_t value) const {
+    uint32_t bits = 0;
+    memcpy(&bits, &value, sizeof(type_t));
+    ptx::st_relaxed_u64(words + tile, ((uint64_t)code << 32) | bits);
+  }
+  MGPU_DEVICE void publish(int tile, uint32_t code) const {
+    ptx::st_relaxed_u64(words + tile, (uint64_t)code << 32);
+  }
+  MGPU_DEVICE uint32_t peek(int tile, type_t& value) const {
+    uint64_t w = ptx::ld_relaxed_u64(words + tile);
+    uint32_t bits = (uint32_t)w;
+    memcpy(&value, &bits, sizeof(type_t));
+    return (uint32_t)(w >> 32);
+  }
+};
+
+template<typename type_t>
+struct tile_state_t<type_t, false> {
+  enum { slot_bytes = tile_state_traits<type_t>::slot_bytes };
+  uint32_t* codes;
+  char* partials;
+  char* inclusives;
+
+  MGPU_DEVICE void bind(void* base, int num_tiles) {
+    size_t n = (size_t)num_tiles;
+    codes = (uint32_t*)base;
+    partials = (char*)base + (n * 4 + 127) / 128 * 128;
+    inclusives = partials + n * slot_bytes;
+  }
+
+  static MGPU_DEVICE void put(char* slot, const type_t& value) {
+    uint32_t tmp[slot_bytes / 4] = { };
+    memcpy(tmp, &value, sizeof(type_t));
+    volatile uint32_t* dst = (volatile uint32_t*)slot;
+    #pragma unroll
+    for(int i = 0; i < slot_bytes / 4; ++i) dst[i] = tmp[i];
+  }
+  static MGPU_DEVICE void take(const char* slot, type_t& value) {
+    uint32_t tmp[slot_bytes / 4];
+    const volatile uint32_t* src = (const volatile uint32_t*)slot;
+    #pragma unroll
+    for(int i = 0; i < slot_bytes / 4; ++i) tmp[i] = src[i];
+    memcpy(&value, tmp, sizeof(type_t));
+  }
+
+  MGPU_DEVICE void publish(int tile, uint32_t code, type_t value) const {
+    char* slot = (tile_partial == code ? partials : inclusives) +
+      (size_t)tile * slot_bytes;
+    put(slot, value);
+    ptx::st_release_u32(codes + tile, code);
+  }
+  MGPU_DEVICE void publish(int tile, uint32_t code) const {
+    ptx::st_release_u32(codes + tile, code);
+  }
+  MGPU_DEVICE uint32_t peek(int tile, type_t& value) const {
+    uint32_t code = ptx::ld_acquire_u32(codes + tile);
+    if(tile_partial == code)
+      take(partials + (size_t)tile * slot_bytes, value);
+    else if(tile_inclusive == code)
+      take(inclusives + (size_t)tile * slot_bytes, value);
+    return code;
+  }
+};
+
+// Lane-to-lane copy of a value of any size.
+template<typename type_t>
+MGPU_DEVICE type_t shfl_any(const type_t& x, int src_lane) {
+  enum { words = (sizeof(type_t) + 3) / 4 };
+  uint32_t w[words] = { };
+  memcpy(w, &x, sizeof(type_t));
+  #pragma unroll
+  for(int i = 0; i < words; ++i)
+    w[i] = __shfl_sync(0xffffffffu, w[i], src_lane);
+  type_t y;
+  memcpy(&y, w, sizeof(type_t));
+  return y;
+}
+template<typename type_t>
+MGPU_DEVICE type_t shfl_up_any(const type_t& x, int delta) {
+  enum { words = (sizeof(type_t) + 3) / 4 };
+  uint32_t w[words] = { };
+  memcpy(w, &x, sizeof(type_t));
+  #pragma unroll
+  for(int i = 0; i < words; ++i)
+    w[i] = __shfl_up_sync(0xffffffffu, w[i], delta);
+  type_t y;
+  memcpy(&y, w, sizeof(type_t));
+  return y;
+}
+
+// Executed by one full warp of tile `tile` (> 0): fold what tiles
+// tile-1, tile-2, ... contribute to the segment that is open at this tile's
+// left edge. Returns true and sets `carry` when there is a contribution.
+// `spin_limit` bounds every wait; on expiry *status is set and false returned.
+template<typename type_t, typename op_t>
+MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
+  op_t op, type_t& carry, uint32_t spin_limit, uint32_t* status) {
+  const unsigned full = 0xffffffffu;
+  int lane = (int)(threadIdx.x & 31);
+  bool have = false;
+  type_t acc = carry;
+  int base = tile - 1;
+  while(true) {
+    int idx = base - lane;
+    uint32_t code = tile_closed;      // before tile 0: nothing to add
+    type_t value = carry;
+    int stop = 32;
+    bool ready = false;
+    for(uint32_t spin = 0; spin < spin_limit; ++spin) {
+      if(idx >= 0) code = state.peek(idx, value);
+      unsigned final_mask = __ballot_sync(full, code >= tile_inclusive);
+      unsigned empty_mask = __ballot_sync(full, tile_empty == code);
+      stop = final_mask ? __ffs(final_mask) - 1 : 32;
+      unsigned needed = stop >= 31 ? full : ((2u << stop) - 1);
+      if(0 == (empty_mask & needed)) { ready = true; break; }
+      if(spin > 16) __nanosleep(100);
+    }
+    if(!ready) {
+      if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);
+      return false;
+    }
+    // Fold lanes last..0 (earliest tile first).
+    int last = stop < 31 ? stop : 31;
+    bool w_have = false;
+    type_t w = value;
+    for(int l = last; l >= 0; --l) {
+      type_t v = shfl_any(value, l);
+      uint32_t c = __shfl_sync(full, code, l);
+      if(tile_closed != c) {
+        w = w_have ? op(w, v) : v;
+        w_have = true;
+      }
+    }
+    if(w_have) {
+      acc = have ? op(w, acc) : w;
+      have = true;
+    }
+    if(stop < 32) break;
+    base -= 32;
+  }
+  if(have) carry = acc;
+  return have;
+}
+
+} // namespace detail
+END_MGPU_NAMESPACE
+
+#endif // __CUDACC__
