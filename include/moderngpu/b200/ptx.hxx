@@ -4,8 +4,9 @@
 // always to the issuing CTA only), named barriers for a subset of a CTA,
 // and scoped loads/stores for the cross-CTA tile-status protocol.
 //
-// Every wait is bounded: it returns false after `spin_limit` polls so the
-// caller can record a status and leave instead of spinning forever.
+// Every wait is bounded by wall-clock time (the %globaltimer register): it
+// returns false once `timeout_ns` has passed, so the caller can record a
+// status and carry on instead of spinning forever.
 #pragma once
 #include "base.hxx"
 
@@ -44,26 +45,36 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar,
     :: "r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 
+// One poll; the thread may stay suspended in hardware for up to ~20 us
+// (a hint) before the instruction reports "not yet".
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
     "{\n"
     "  .reg .pred p;\n"
-    "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+    "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
     "  selp.u32 %0, 1, 0, p;\n"
     "}\n"
-    : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    : "=r"(done) : "r"(smem_addr(bar)), "r"(parity), "r"(20000u) : "memory");
   return done != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
 
 // Bounded wait for the phase with the given parity to complete.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-  uint32_t spin_limit) {
-  for(uint32_t spin = 0; spin < spin_limit; ++spin) {
-    if(mbar_try_wait(bar, parity)) return true;
-    if(spin > 64) __nanosleep(64);
+  uint64_t timeout_ns) {
+  if(mbar_try_wait(bar, parity)) return true;
+  uint64_t start = global_timer_ns();
+  while(true) {
+    for(int spin = 0; spin < 32; ++spin)
+      if(mbar_try_wait(bar, parity)) return true;
+    if(global_timer_ns() - start > timeout_ns) return false;
   }
-  return false;
 }
 
 ////////////////////////////////////////////////////////////////////////////////

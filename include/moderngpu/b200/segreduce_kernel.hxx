@@ -68,7 +68,7 @@ struct segreduce_default_tuning<type_t, 1> { typedef segreduce_tuning_t<256, 16,
 template<typename type_t>
 struct segreduce_default_tuning<type_t, 2> { typedef segreduce_tuning_t<256, 16, 3, 3> type; };
 template<typename type_t>
-struct segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<256, 20, 3, 3> type; };
+struct segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<256, 28, 2, 3> type; };
 template<typename type_t>
 struct segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 10, 3, 3> type; };
 template<typename type_t>
@@ -137,7 +137,26 @@ struct segreduce_args_t {
   const int* partitions;
   uint32_t* header;       // [0] ticket counter, [1] status
   void* tile_state;
-  uint32_t spin_limit;
+  uint64_t timeout_ns;    // bound on every device-side wait
+};
+
+// A finished tile hands the one output that may need earlier tiles, and the
+// publication of its inclusive value when it holds no segment start, to the
+// CTA's carry warp through a small ring of these records.
+template<typename type_t>
+struct carry_req_t {
+  int tile;          // -1: no more requests
+  int flags;         // carry_* bits below
+  int out_index;     // output[] element to write when carry_out is set
+  int pad;
+  alignas(8) char lead[sizeof(type_t)];   // fold of the tile's leading run
+  alignas(8) char tail[sizeof(type_t)];   // fold of all the tile's items
+};
+enum {
+  carry_out = 1,        // write output[out_index]
+  carry_has_lead = 2,   // the leading run has items in this tile
+  carry_need_left = 4,  // the segment began in an earlier tile
+  carry_partial = 8     // the tile published tile_partial
 };
 
 template<typename tuning_t, typename type_t>
@@ -148,12 +167,16 @@ struct segreduce_smem_t {
     flag_words = nt * vt / 32 + 2,
     elem = (int)sizeof(type_t),
     wide = elem > 4 ? elem : 4,
-    stage_bytes = (nv * wide + 8 * elem + 64 + 127) / 128 * 128
+    stage_bytes = (nv * wide + 8 * elem + 64 + 127) / 128 * 128,
+    ring = 4
   };
   struct fixed_t {
     uint64_t full[stages];
     uint64_t empty[stages];
+    uint64_t req_full[ring];
+    uint64_t req_empty[ring];
     tile_desc_t desc[stages];
+    carry_req_t<type_t> req[ring];
     uint32_t flags[2][flag_words];
     int warp_head[warps];
     alignas(16) char warp_agg[warps * elem];
@@ -183,7 +206,7 @@ MGPU_DEVICE void load_chunk(const type_t* src, type_t (&v)[vt]) {
 
 template<typename tuning_t, typename type_t, typename source_t,
   typename segments_it, typename output_it, typename op_t>
-__global__ void __launch_bounds__(tuning_t::nt + 32, tuning_t::occ)
+__global__ void __launch_bounds__(tuning_t::nt + 64, tuning_t::occ)
 segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   op_t> args) {
 
@@ -192,6 +215,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   enum { nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
     nv = tuning_t::nv, warps = nt / 32, flag_words = layout_t::flag_words,
     elem = layout_t::elem, stage_bytes = layout_t::stage_bytes,
+    ring = layout_t::ring,
     src_bulk = source_t::bulk,
     seg_bulk = segments_are_int_array<segments_it>::value };
 
@@ -212,38 +236,60 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       ptx::mbar_init(&fixed.empty[s], nt);
       fixed.desc[s].tile = -1;
     }
+    for(int r = 0; r < ring; ++r) {
+      ptx::mbar_init(&fixed.req_full[r], 1);
+      ptx::mbar_init(&fixed.req_empty[r], 1);
+    }
     ptx::fence_proxy_async();
   }
-  for(int i = tid; i < 2 * flag_words; i += nt + 32)
+  for(int i = tid; i < 2 * flag_words; i += nt + 64)
     (&fixed.flags[0][0])[i] = 0;
   __syncthreads();
 
   //////////////////////////////////////////////////////////////////////////////
-  // Producer warp.
+  // Producer warp: tickets, partition lookups, bulk copies.
 
   if(warp == warps) {
     if(lane) return;
     const int64_t total = (int64_t)count + num_segments;
+    // The next ticket and its two partition values are fetched one
+    // iteration ahead, so their latency hides behind the wait for a free
+    // stage buffer.
+    int next_tile = (int)atomicAdd(args.header, 1u);
+    int next_a0 = 0, next_a1 = 0;
+    if(next_tile < num_tiles) {
+      next_a0 = args.partitions[next_tile];
+      next_a1 = args.partitions[next_tile + 1];
+    }
     for(int it = 0; ; ++it) {
       int s = it % stages;
       int use = it / stages;
       if(use > 0 &&
-        !ptx::mbar_wait(&fixed.empty[s], (use - 1) & 1, args.spin_limit))
+        !ptx::mbar_wait(&fixed.empty[s], (use - 1) & 1, args.timeout_ns))
         atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
 
       tile_desc_t d;
-      d.tile = (int)atomicAdd(args.header, 1u);
+      d.tile = next_tile;
       if(d.tile >= num_tiles) {
         fixed.desc[s].tile = -1;
         ptx::mbar_arrive(&fixed.full[s]);
         break;
       }
-      d.a0 = args.partitions[d.tile];
-      d.a1 = args.partitions[d.tile + 1];
+      d.a0 = next_a0;
+      d.a1 = next_a1;
       int64_t d0 = (int64_t)d.tile * nv;
       int64_t d1 = d0 + nv < total ? d0 + nv : total;
-      d.b0 = (int)(d0 - d.a0);
-      d.b1 = (int)(d1 - d.a1);
+      // No-ops for valid input; offsets that are not sorted or exceed count
+      // give wrong results but must never index outside the arrays.
+      d.a0 = d.a0 < 0 ? 0 : (d.a0 > count ? count : d.a0);
+      d.a1 = d.a1 < d.a0 ? d.a0 : (d.a1 > count ? count : d.a1);
+      if(d.a1 - d.a0 > nv) d.a1 = d.a0 + nv;
+      int64_t b0 = d0 - d.a0, b1 = d1 - d.a1;
+      b0 = b0 < 0 ? 0 : (b0 > num_segments ? num_segments : b0);
+      b1 = b1 < b0 ? b0 : (b1 > num_segments ? num_segments : b1);
+      if(b1 - b0 > nv) b1 = b0 + nv;
+      d.b0 = (int)b0;
+      d.b1 = (int)b1;
       d.pad = 0;
       char* stage = stage_base + s * stage_bytes;
       int na = d.a1 - d.a0;
@@ -319,6 +365,54 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       } else {
         ptx::mbar_arrive(&fixed.full[s]);
       }
+
+      next_tile = (int)atomicAdd(args.header, 1u);
+      if(next_tile < num_tiles) {
+        next_a0 = args.partitions[next_tile];
+        next_a1 = args.partitions[next_tile + 1];
+      }
+    }
+    return;
+  }
+
+  op_t op = args.op;
+  const type_t init = args.init;
+  tile_state_t<type_t> state;
+  state.bind(args.tile_state, num_tiles);
+
+  //////////////////////////////////////////////////////////////////////////////
+  // Carry warp: finishes, off the consumers' critical path, whatever needs
+  // values of earlier tiles.
+
+  if(warp == warps + 1) {
+    for(int n = 0; ; ++n) {
+      int r = n % ring;
+      if(!ptx::mbar_wait(&fixed.req_full[r], (n / ring) & 1, args.timeout_ns))
+        atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+      carry_req_t<type_t> req = fixed.req[r];
+      __syncwarp();
+      if(0 == lane) ptx::mbar_arrive(&fixed.req_empty[r]);
+      if(req.tile < 0) break;
+
+      type_t lead, tail;
+      memcpy(&lead, req.lead, sizeof(type_t));
+      memcpy(&tail, req.tail, sizeof(type_t));
+      bool have = false;
+      type_t carry = init;
+      if(req.tile > 0 && (req.flags & (carry_need_left | carry_partial)))
+        have = lookback(state, req.tile, op, carry, args.timeout_ns,
+          args.header + 1);
+      if(0 == lane) {
+        if(req.flags & carry_partial)
+          state.publish(req.tile, tile_inclusive,
+            have ? op(carry, tail) : tail);
+        if(req.flags & carry_out) {
+          type_t result = lead;
+          if((req.flags & carry_need_left) && have)
+            result = (req.flags & carry_has_lead) ? op(carry, lead) : carry;
+          args.output[req.out_index] = result;
+        }
+      }
     }
     return;
   }
@@ -326,17 +420,25 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   //////////////////////////////////////////////////////////////////////////////
   // Consumers.
 
-  op_t op = args.op;
-  const type_t init = args.init;
-  tile_state_t<type_t> state;
-  state.bind(args.tile_state, num_tiles);
   type_t* warp_agg = reinterpret_cast<type_t*>(fixed.warp_agg);
   const unsigned full_mask = 0xffffffffu;
   const uint32_t vt_mask = (1u << vt) - 1;
+  int requests = 0;     // used by thread 0 only
+
+  auto send_request = [&](const carry_req_t<type_t>& req) {
+    int r = requests % ring;
+    int use = requests / ring;
+    if(use > 0 &&
+      !ptx::mbar_wait(&fixed.req_empty[r], (use - 1) & 1, args.timeout_ns))
+      atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+    fixed.req[r] = req;
+    ptx::mbar_arrive(&fixed.req_full[r]);
+    ++requests;
+  };
 
   for(int it = 0; ; ++it) {
     int s = it % stages;
-    if(!ptx::mbar_wait(&fixed.full[s], (it / stages) & 1, args.spin_limit))
+    if(!ptx::mbar_wait(&fixed.full[s], (it / stages) & 1, args.timeout_ns))
       atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
     const tile_desc_t d = fixed.desc[s];
     if(d.tile < 0) break;
@@ -361,6 +463,11 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       if(j >= ob && j < oe) return offs[j - ob];
       return (int)args.segments[j];
     };
+    // Same, when every offset this tile touches is staged (the usual case).
+    const int* offs_by_seg = offs - ob;
+    auto seg_start_staged = [&](int j) -> int { return offs_by_seg[j]; };
+    const bool all_staged = !is_last && (b0 > 0 ? b0 - 1 : 0) >= ob &&
+      b1 <= oe;
 
     if constexpr (!src_bulk) {
       for(int i = tid; i < na; i += nt) vals[i] = args.source.load(a0 + i);
@@ -372,42 +479,60 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     }
 
     // 1. Head flags, and `init` for empty segments.
-    for(int j = b0 + tid; j < jend; j += nt) {
-      int p = seg_start(j);
-      if(j < b1) {
-        int rel = p - a0;
-        rel = rel < 0 ? 0 : (rel > na ? na : rel);
-        int w = lo + rel;
-        atomicOr(&flags[w >> 5], 1u << (w & 31));
+    auto mark_heads = [&](auto start_of) {
+      for(int j = b0 + tid; j < jend; j += nt) {
+        int p = start_of(j);
+        if(j < b1) {
+          int rel = p - a0;
+          rel = rel < 0 ? 0 : (rel > na ? na : rel);
+          int w = lo + rel;
+          atomicOr(&flags[w >> 5], 1u << (w & 31));
+        }
+        if(j > 0 && start_of(j - 1) == p) args.output[j - 1] = init;
       }
-      if(j > 0 && seg_start(j - 1) == p) args.output[j - 1] = init;
-    }
+    };
+    if(all_staged) mark_heads(seg_start_staged);
+    else mark_heads(seg_start);
     if(0 == tid) {
+      // Sentinels: the tile's right edge always ends a run, and a head at
+      // the first item keeps padding to its left out of every fold.
       atomicOr(&flags[hi >> 5], 1u << (hi & 31));
+      if(lo) atomicOr(&flags[lo >> 5], 1u << (lo & 31));
       if(0 == na) state.publish(d.tile, tile_closed);
     }
     ptx::named_sync<1, nt>();
 
     if(na > 0) {
-      // 2. Per-thread fold of positions [w0, w0 + vt).
+      // 2. Per-thread fold of positions [w0, w0 + vt). The value of every
+      // run that ends inside the thread's range is stored in place; the
+      // first of them still lacks what precedes the thread (step 4).
+      // For arithmetic types the unrolled path also serves the threads that
+      // straddle the tile's edges: padding positions hold arbitrary bits
+      // whose folds are never stored or propagated, thanks to the sentinels.
       const int w0 = tid * vt;
-      const bool fast = w0 >= lo && w0 + vt <= hi &&
-        w0 >= d.src_lo && w0 + vt <= d.src_hi;
       int i_lo = lo > w0 ? lo - w0 : 0;
       int i_hi = hi - w0 < vt ? hi - w0 : vt;
+      const bool inside = w0 + i_lo >= d.src_lo && w0 + i_hi <= d.src_hi;
+      const bool fast = std::is_arithmetic<type_t>::value ?
+        (i_lo < i_hi && inside) : (inside && 0 == i_lo && vt == i_hi);
       uint32_t bits = __funnelshift_r(flags[w0 >> 5], flags[(w0 >> 5) + 1],
         w0 & 31);
+      uint32_t ends = bits >> 1;
 
-      type_t v[vt];
       type_t x = init;
       bool head = true;
       if(fast) {
+        type_t v[vt];
         load_chunk<vt>(vals + w0, v);
         x = v[0];
+        if(ends & 1) vals[w0] = x;
         #pragma unroll
-        for(int i = 1; i < vt; ++i)
+        for(int i = 1; i < vt; ++i) {
           x = ((bits >> i) & 1) ? v[i] : op(x, v[i]);
+          if((ends >> i) & 1) vals[w0 + i] = x;
+        }
         head = 0 != (bits & vt_mask);
+        ends &= vt_mask;
       } else if(i_lo < i_hi) {
         if constexpr (src_bulk) {
           // Array elements outside the 16-byte-aligned interior.
@@ -418,14 +543,21 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           }
         }
         x = vals[w0 + i_lo];
+        if((ends >> i_lo) & 1) vals[w0 + i_lo] = x;
         for(int i = i_lo + 1; i < i_hi; ++i) {
           type_t y = vals[w0 + i];
           x = ((bits >> i) & 1) ? y : op(x, y);
+          if((ends >> i) & 1) vals[w0 + i] = x;
         }
-        uint32_t range = (i_hi >= 32 ? full_mask : ((1u << i_hi) - 1)) &
-          ~((1u << i_lo) - 1);
+        uint32_t range = ((1u << i_hi) - 1) & ~((1u << i_lo) - 1);
         head = 0 != (bits & range);
+        ends &= range;
+      } else {
+        ends = 0;
       }
+      // Does the thread's first run start at a head of its own?
+      const int first_item = fast ? 0 : i_lo;
+      const bool first_is_head = (bits >> first_item) & 1;
 
       // 3. Segmented scan of (head, x) across the CTA.
       unsigned head_mask = __ballot_sync(full_mask, head);
@@ -437,58 +569,38 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         type_t y = shfl_up_any(incl, delta);
         if(lane - delta >= run_start) incl = op(y, incl);
       }
-      type_t from_left = shfl_up_any(incl, 1);
+      type_t c = shfl_up_any(incl, 1);
       if(31 == lane) {
         warp_agg[warp] = incl;
         fixed.warp_head[warp] = 0 != head_mask;
       }
       ptx::named_sync<1, nt>();
 
-      bool head_before = 0 != (head_mask & ((1u << lane) - 1));
-      bool has_c = lane > 0;
-      type_t c = from_left;
-      if(!head_before && warp > 0) {
-        // The run reaching this thread began in an earlier warp.
-        type_t cw = warp_agg[warp - 1];
-        for(int k = warp - 1; k > 0 && !fixed.warp_head[k]; --k)
-          cw = op(warp_agg[k - 1], cw);
-        c = has_c ? op(cw, c) : cw;
-        has_c = true;
-      }
-
-      // 4. Values at segment ends, stored in place; the open segment's value
-      // at the right edge goes to the tile-status array.
-      uint32_t ends = bits >> 1;
-      type_t y = init;
-      bool at_edge = false;
-      if(fast) {
-        if(ends & vt_mask) {
-          y = ((bits & 1) || !has_c) ? v[0] : op(c, v[0]);
-          if(ends & 1) vals[w0] = y;
-          #pragma unroll
-          for(int i = 1; i < vt; ++i) {
-            y = ((bits >> i) & 1) ? v[i] : op(y, v[i]);
-            if((ends >> i) & 1) vals[w0 + i] = y;
-          }
-          at_edge = w0 + vt == hi;
+      // 4. Complete the first run end of each thread with what precedes it.
+      if(ends && !first_is_head) {
+        bool has_c = lane > 0;
+        bool head_before = 0 != (head_mask & ((1u << lane) - 1));
+        if(!head_before && warp > 0) {
+          type_t cw = warp_agg[warp - 1];
+          for(int k = warp - 1; k > 0 && !fixed.warp_head[k]; --k)
+            cw = op(warp_agg[k - 1], cw);
+          c = has_c ? op(cw, c) : cw;
+          has_c = true;
         }
-      } else if(i_lo < i_hi) {
-        type_t first = vals[w0 + i_lo];
-        y = (((bits >> i_lo) & 1) || !has_c) ? first : op(c, first);
-        if((ends >> i_lo) & 1) vals[w0 + i_lo] = y;
-        for(int i = i_lo + 1; i < i_hi; ++i) {
-          type_t z = vals[w0 + i];
-          y = ((bits >> i) & 1) ? z : op(y, z);
-          if((ends >> i) & 1) vals[w0 + i] = y;
+        if(has_c) {
+          int e1 = w0 + __ffs(ends) - 1;
+          vals[e1] = op(c, vals[e1]);
         }
-        at_edge = w0 + i_hi == hi;
       }
-      if(at_edge) {
+      // The thread that owns the last item publishes the tile's state.
+      if(hi - 1 >= w0 && hi - 1 < w0 + vt) {
         uint32_t code;
-        if(nb > 0) code = seg_start(b1 - 1) == a1 ? tile_closed :
-          tile_inclusive;
-        else code = d.tile ? tile_partial : tile_inclusive;
-        state.publish(d.tile, code, y);
+        if(nb > 0) {
+          int p_last = all_staged ? seg_start_staged(b1 - 1) :
+            seg_start(b1 - 1);
+          code = p_last == a1 ? tile_closed : tile_inclusive;
+        } else code = d.tile ? tile_partial : tile_inclusive;
+        state.publish(d.tile, code, vals[hi - 1]);
       }
     }
 
@@ -496,51 +608,56 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     ptx::named_sync<1, nt>();
 
     // 5. Outputs of the segments that end in this tile. The first one may
-    // need items of earlier tiles and is finished by warp 0 below.
-    const bool first_valid = b0 >= 1 && b0 < jend;
-    int prev0 = 0, p0 = 0;
-    bool need_out = false;
-    if(first_valid) {
-      prev0 = seg_start(b0 - 1);
-      p0 = seg_start(b0);
-      need_out = prev0 != p0;
-    }
-    const bool partial_tile = 0 == nb && d.tile > 0;
-    int q0 = p0 - a0;
-    q0 = q0 < 0 ? 0 : (q0 > na ? na : q0);
-    type_t lead = init, tail = init;
-    if(0 == warp) {
-      if(need_out && q0 > 0) lead = vals[lo + q0 - 1];
-      if(partial_tile) tail = vals[hi - 1];
-    }
-    for(int j = b0 + 1 + tid; j < jend; j += nt) {
-      int p = seg_start(j);
-      if(seg_start(j - 1) != p) {
-        int rel = p - a0;
-        rel = rel < 1 ? 1 : (rel > na ? na : rel);
-        args.output[j - 1] = vals[lo + rel - 1];
-      }
-    }
-    ptx::fence_proxy_async();
-    ptx::mbar_arrive(&fixed.empty[s]);
-
-    if(0 == warp) {
-      bool need_carry = need_out && prev0 < a0 && d.tile > 0;
-      bool have = false;
-      type_t carry = init;
-      if(need_carry || partial_tile)
-        have = lookback(state, d.tile, op, carry, args.spin_limit,
-          args.header + 1);
-      if(0 == lane) {
-        if(partial_tile)
-          state.publish(d.tile, tile_inclusive, have ? op(carry, tail) : tail);
-        if(need_out) {
-          type_t r = lead;
-          if(need_carry && have) r = q0 > 0 ? op(carry, lead) : carry;
-          args.output[b0 - 1] = r;
+    // need items of earlier tiles: that one goes to the carry warp.
+    carry_req_t<type_t> req;
+    if(0 == tid) {
+      req.tile = d.tile;
+      req.flags = 0;
+      req.out_index = b0 - 1;
+      req.pad = 0;
+      type_t lead = init, tail = init;
+      if(b0 >= 1 && b0 < jend) {
+        int prev0 = seg_start(b0 - 1);
+        int p0 = seg_start(b0);
+        if(prev0 != p0) {
+          req.flags |= carry_out;
+          int q0 = p0 - a0;
+          q0 = q0 < 0 ? 0 : (q0 > na ? na : q0);
+          if(q0 > 0) {
+            req.flags |= carry_has_lead;
+            lead = vals[lo + q0 - 1];
+          }
+          if(prev0 < a0) req.flags |= carry_need_left;
         }
       }
+      if(0 == nb && d.tile > 0) {
+        req.flags |= carry_partial;
+        tail = vals[hi - 1];
+      }
+      memcpy(req.lead, &lead, sizeof(type_t));
+      memcpy(req.tail, &tail, sizeof(type_t));
     }
+    auto write_outputs = [&](auto start_of) {
+      for(int j = b0 + 1 + tid; j < jend; j += nt) {
+        int p = start_of(j);
+        if(start_of(j - 1) != p) {
+          int rel = p - a0;
+          rel = rel < 1 ? 1 : (rel > na ? na : rel);
+          args.output[j - 1] = vals[lo + rel - 1];
+        }
+      }
+    };
+    if(all_staged) write_outputs(seg_start_staged);
+    else write_outputs(seg_start);
+    ptx::fence_proxy_async();
+    ptx::mbar_arrive(&fixed.empty[s]);
+    if(0 == tid && req.flags) send_request(req);
+  }
+  if(0 == tid) {
+    carry_req_t<type_t> req;
+    memset(&req, 0, sizeof(req));
+    req.tile = -1;
+    send_request(req);
   }
 }
 
@@ -584,7 +701,8 @@ int resident_ctas(kernel_t kernel, int threads, int smem_bytes) {
   return n;
 }
 
-enum : uint32_t { default_spin_limit = 1u << 24 };
+// Default bound on device-side waits: two seconds.
+constexpr uint64_t default_timeout_ns = 2000000000ull;
 
 // Enqueue partitioner + reduction on `stream`. `workspace` must hold
 // segreduce_plan_t<...>(count, num_segments).bytes bytes, 128-byte aligned.
@@ -592,7 +710,7 @@ template<typename tuning_t, typename type_t, typename source_t,
   typename segments_it, typename output_it, typename op_t>
 void segreduce_enqueue(source_t source, int count, segments_it segments,
   int num_segments, output_it output, op_t op, type_t init, void* workspace,
-  cudaStream_t stream, uint32_t spin_limit = default_spin_limit) {
+  cudaStream_t stream, uint64_t timeout_ns = default_timeout_ns) {
 
   typedef segreduce_smem_t<tuning_t, type_t> layout_t;
   typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t>
@@ -612,13 +730,13 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
 
   auto kernel = segreduce_k<tuning_t, type_t, source_t, segments_it,
     output_it, op_t>;
-  int threads = tuning_t::nt + 32;
+  int threads = tuning_t::nt + 64;
   int resident = resident_ctas<tuple<tuning_t, args_t> >(kernel, threads,
     (int)layout_t::total_bytes);
   int grid = plan.num_tiles < resident ? plan.num_tiles : resident;
 
   args_t args { source, segments, output, op, init, count, num_segments,
-    plan.num_tiles, partitions, header, state, spin_limit };
+    plan.num_tiles, partitions, header, state, timeout_ns };
   kernel<<<grid, threads, layout_t::total_bytes, stream>>>(args);
 }
 

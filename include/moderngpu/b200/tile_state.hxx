@@ -162,10 +162,10 @@ MGPU_DEVICE type_t shfl_up_any(const type_t& x, int delta) {
 // Executed by one full warp of tile `tile` (> 0): fold what tiles
 // tile-1, tile-2, ... contribute to the segment that is open at this tile's
 // left edge. Returns true and sets `carry` when there is a contribution.
-// `spin_limit` bounds every wait; on expiry *status is set and false returned.
+// `timeout_ns` bounds every wait; on expiry *status is set and false returned.
 template<typename type_t, typename op_t>
 MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
-  op_t op, type_t& carry, uint32_t spin_limit, uint32_t* status) {
+  op_t op, type_t& carry, uint64_t timeout_ns, uint32_t* status) {
   const unsigned full = 0xffffffffu;
   int lane = (int)(threadIdx.x & 31);
   bool have = false;
@@ -177,7 +177,8 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
     type_t value = carry;
     int stop = 32;
     bool ready = false;
-    for(uint32_t spin = 0; spin < spin_limit; ++spin) {
+    uint64_t start = 0;
+    for(uint32_t spin = 0; ; ++spin) {
       if(idx >= 0) code = state.peek(idx, value);
       unsigned final_mask = __ballot_sync(full, code >= tile_inclusive);
       unsigned empty_mask = __ballot_sync(full, tile_empty == code);
@@ -185,6 +186,12 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
       unsigned needed = stop >= 31 ? full : ((2u << stop) - 1);
       if(0 == (empty_mask & needed)) { ready = true; break; }
       if(spin > 16) __nanosleep(100);
+      if(31 == (spin & 31)) {
+        // Lane 0's clock decides for the whole warp.
+        uint64_t now = __shfl_sync(full, ptx::global_timer_ns(), 0);
+        if(!start) start = now;
+        else if(now - start > timeout_ns) break;
+      }
     }
     if(!ready) {
       if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);

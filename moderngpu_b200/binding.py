@@ -70,8 +70,8 @@ def load_library():
     lib.mgpu_b200_load_balance_partitions.restype = c_int
     lib.mgpu_b200_load_balance_partitions.argtypes = [
         c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
-    lib.mgpu_b200_debug_set_spin_limit.restype = ctypes.c_uint32
-    lib.mgpu_b200_debug_set_spin_limit.argtypes = [ctypes.c_uint32]
+    lib.mgpu_b200_debug_set_wait_limit_ns.restype = ctypes.c_uint64
+    lib.mgpu_b200_debug_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     _declare_optional(lib)
     _lib = lib
     return lib

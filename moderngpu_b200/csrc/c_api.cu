@@ -13,10 +13,9 @@ inline int cuda_code(cudaError_t e) {
 
 inline int last_launch_code() { return cuda_code(cudaGetLastError()); }
 
-// Bound on every device-side wait, in polls (each poll sleeps ~100 ns once
-// the first few have failed). Adjustable so that tests can make a wait run
-// out quickly without hanging anything.
-uint32_t g_spin_limit = detail::default_spin_limit;
+// Bound on every device-side wait, in nanoseconds. Adjustable so that tests
+// can make a wait run out quickly without hanging anything.
+uint64_t g_timeout_ns = detail::default_timeout_ns;
 
 template<typename type_t>
 struct type_tuning { typedef typename detail::segreduce_default_tuning<type_t>::type type; };
@@ -38,7 +37,7 @@ int segreduce_typed(const void* input, int count, const int* segments,
   detail::array_source_t<type_t> source { (const type_t*)input };
   try {
     detail::segreduce_enqueue<tuning_t>(source, count, segments, num_segments,
-      (type_t*)output, op_t(), init, workspace, stream, g_spin_limit);
+      (type_t*)output, op_t(), init, workspace, stream, g_timeout_ns);
   } catch(cuda_exception_t& e) {
     return cuda_code(e.result);
   }
@@ -87,11 +86,12 @@ const char* mgpu_b200_error_string(int code) {
   return "unknown error";
 }
 
-// Test hook: bound, in polls, on every device-side wait of later calls.
-// Returns the previous value. Not part of the stable interface.
-uint32_t mgpu_b200_debug_set_spin_limit(uint32_t polls) {
-  uint32_t old = g_spin_limit;
-  g_spin_limit = polls ? polls : detail::default_spin_limit;
+// Test hook: bound, in nanoseconds, on every device-side wait of later calls
+// (0 restores the default). Returns the previous value. Not part of the
+// stable interface.
+uint64_t mgpu_b200_debug_set_wait_limit_ns(uint64_t ns) {
+  uint64_t old = g_timeout_ns;
+  g_timeout_ns = ns ? ns : detail::default_timeout_ns;
   return old;
 }
 
