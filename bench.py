@@ -1,0 +1,434 @@
+#!/usr/bin/env python
+"""Benchmark of the segmented-reduction hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-cuda]
+
+A step is one mgpu segreduce over one batch of synthetic input: fp32 plus over
+268,435,456 items uniform in [-1, 1) in 8,388,608 segments with geometric
+lengths (mean 32, 5 % empty), init 0 -- per GPU. With N > 1 (launched by
+torch.distributed.run, one rank per GPU) every rank holds such a shard of one
+N-times larger array, segments straddle the shard boundaries, and each step
+also exchanges and folds the boundary partials (weak scaling).
+
+Rank 0 prints ONE JSON line: `value` is whole-job Gitems/s with inputs
+resident in HBM (CUDA events on the launching stream, max over ranks), `e2e`
+the same metric through the host-buffer entry point of the C ABI (pinned host
+inputs, host<->device copies inside the timed region), `roofline` the dominant
+kernel against the measured HBM copy bandwidth, `cpu_baseline` the CPU oracle
+timed on the host cores.
+
+--impl reference times the reference's host loop (tests/test_segreduce.cu:
+40-49, restated in oracle/oracle.c) on all host cores; --impl reference-cuda
+times the reference's own CUDA build (oracle/_ref/libmgpu_ref.so) on the GPU.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+COUNT = 1 << 28
+NUM_SEGMENTS = 1 << 23
+METRIC = "segreduce_throughput_256M_fp32_items"
+UNIT = "Gitems/s"
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of the reduction kernel from
+# one ncu capture of a 2^26-item case of the same workload
+# (profiles/segreduce_k_fp32_c2.md), divided by that case's algorithmic
+# bytes; DRAM traffic grows in proportion to the units processed.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0026
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while running."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,"
+             "clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index),
+                 "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [],
+                    "note": "nvidia-smi unavailable"}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                 "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                smax.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(count=1 << 26, num_segments=1 << 21, seed=1):
+    """A bounded sample of the workload for the CPU arm, generated on the host
+    with the same length and value distributions."""
+    import torch
+    from moderngpu_b200 import workloads
+    values, seg = workloads.config2(seed=seed, count=count,
+                                    num_segments=num_segments, device="cpu")
+    return values.numpy(), seg.numpy()
+
+
+def time_cpu(values, seg, budget_s, threads):
+    import oracle
+    oracle.segreduce(values[:1 << 20], seg[:1 << 10], threads=threads)
+    reps, spent = 0, 0.0
+    while spent < budget_s and reps < 100000:
+        t0 = time.perf_counter()
+        oracle.segreduce(values, seg, op="plus", init=0.0, threads=threads)
+        spent += time.perf_counter() - t0
+        reps += 1
+    return values.size * reps / spent / 1e9, reps, spent
+
+
+def run_reference_cpu(args, rank, world):
+    if rank != 0:
+        return
+    import oracle
+    values, seg = cpu_sample()
+    threads = oracle.max_threads()
+    oracle.segreduce(values, seg, threads=threads)        # warm
+    for _ in range(max(args.warmup - 1, 0)):
+        oracle.segreduce(values, seg, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.segreduce(values, seg, op="plus", init=0.0, threads=threads)
+    dt = time.perf_counter() - t0
+    value = values.size * args.steps / dt / 1e9
+    sample = ("each step: host loop of tests/test_segreduce.cu:40-49 (C port, "
+              "OpenMP over segments) on a %d-item / %d-segment sample of the "
+              "workload" % (values.size, seg.size))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads,
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "config 2: fp32 plus-segreduce, 268,435,456 items uniform "
+                    "in [-1,1), 8,388,608 segments, geometric lengths mean 32 "
+                    "with 5% empty, init 0 (per GPU)",
+        "items_per_gpu": COUNT, "segments_per_gpu": NUM_SEGMENTS,
+        "sharding": "item range cut evenly over %d GPU(s); one 16-byte "
+                    "boundary record per GPU exchanged per step" % n_gpus,
+        "l2": "inputs are 1.14 GB per GPU, larger than the 126 MB L2; no "
+              "flush between steps",
+    }
+
+
+def run_reference_cuda(args, rank, world):
+    if rank != 0:
+        return
+    import torch
+    from moderngpu_b200 import workloads
+    path = os.path.join(ROOT, "oracle", "_ref", "libmgpu_ref.so")
+    if not os.path.exists(path):
+        print(json.dumps({"impl": "reference-cuda", "unavailable":
+                          "oracle/_ref/libmgpu_ref.so was not built"}))
+        return
+    ref = ctypes.CDLL(path)
+    torch.cuda.set_device(0)
+    values, seg = workloads.config2(seed=1, count=COUNT,
+                                    num_segments=NUM_SEGMENTS)
+    out = torch.empty(NUM_SEGMENTS, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+
+    def call(pooled, sync):
+        code = ref.ref_segreduce_f32(
+            ctypes.c_void_p(values.data_ptr()), COUNT,
+            ctypes.c_void_p(seg.data_ptr()), NUM_SEGMENTS,
+            ctypes.c_void_p(out.data_ptr()), ctypes.c_float(0), 0, pooled, sync)
+        assert code == 0, "reference returned CUDA error %d" % code
+
+    results = {}
+    for pooled in (0, 1):
+        for _ in range(max(args.warmup, 3)):
+            call(pooled, 1)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            call(pooled, 0)
+        torch.cuda.synchronize()
+        results[pooled] = (time.perf_counter() - t0) / args.steps
+    hv = values.cpu().pin_memory()
+    hs = seg.cpu().pin_memory()
+    ho = torch.empty(NUM_SEGMENTS, dtype=torch.float32).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        ref.ref_segreduce_f32_host(ctypes.c_void_p(hv.data_ptr()), COUNT,
+                                   ctypes.c_void_p(hs.data_ptr()), NUM_SEGMENTS,
+                                   ctypes.c_void_p(ho.data_ptr()),
+                                   ctypes.c_float(0))
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        ref.ref_segreduce_f32_host(ctypes.c_void_p(hv.data_ptr()), COUNT,
+                                   ctypes.c_void_p(hs.data_ptr()), NUM_SEGMENTS,
+                                   ctypes.c_void_p(ho.data_ptr()),
+                                   ctypes.c_float(0))
+    e2e_t = (time.perf_counter() - t0) / e2e_steps
+    line = {
+        "impl": "reference-cuda", "metric": METRIC,
+        "value": COUNT / results[0] / 1e9, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": results[0] * 1e3, "higher_is_better": True,
+        "dtype": "f32", "data": "synthetic", "config": workload_config(1),
+        "note": "unmodified moderngpu headers compiled for sm_100a; value = "
+                "stock standard_context_t (cudaMalloc/cudaFree per call), "
+                "host-clock timed; pooled_context = same kernels with "
+                "recycled temporaries",
+        "pooled_context": {"value": COUNT / results[1] / 1e9, "unit": UNIT,
+                           "ms_per_step": results[1] * 1e3},
+        "e2e": {"value": COUNT / e2e_t / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": COUNT * 4 + NUM_SEGMENTS * 4,
+                "d2h_bytes_per_step": NUM_SEGMENTS * 4},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def make_shard(rank, device):
+    """This rank's shard: values and shard-local start table (entry 0 is the
+    virtual start that stands for the segment carried in from the left)."""
+    import torch
+    from moderngpu_b200 import workloads
+    values, seg = workloads.config2(seed=1 + rank, count=COUNT,
+                                    num_segments=NUM_SEGMENTS, device=device)
+    if rank > 0:
+        # The first real segment starts a little into the shard: the leading
+        # items continue the previous rank's last segment.
+        lead = 17 + rank
+        seg = torch.clamp(seg + lead, max=COUNT)
+    table = torch.cat([torch.zeros(1, dtype=torch.int32, device=device), seg])
+    return values, seg, table
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import moderngpu_b200 as mgpu
+    from moderngpu_b200 import sharded, workloads
+
+    mgpu.load_library()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    values, seg, table = make_shard(rank, device)
+    out = torch.empty(NUM_SEGMENTS, dtype=torch.float32, device=device)
+    records = torch.empty(world * sharded.RECORD_BYTES, dtype=torch.uint8,
+                          device=device)
+
+    def step():
+        if world == 1:
+            mgpu.segreduce(values, seg, op="plus", init=0.0, out=out)
+        else:
+            sharded.sharded_segreduce(values, table, op="plus", init=0.0,
+                                      records=records)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    assert mgpu.workspace_status() == 0, "device-side status reported failure"
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    torch.cuda.synchronize()
+    elapsed_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+        dist.barrier()
+    ms_per_step = elapsed_ms / args.steps
+    value = world * COUNT / (ms_per_step * 1e-3) / 1e9
+
+    # Dominant kernel alone, timed live with CUDA events between the two
+    # launches of a call (rank 0's GPU).
+    roofline = None
+    if rank == 0:
+        reduce_ms, part_ms = [], []
+        for _ in range(min(max(args.steps, 3), 10)):
+            _, p_ms, r_ms = mgpu.segreduce_profile(values, seg, op="plus",
+                                                   init=0.0, out=out)
+            part_ms.append(p_ms)
+            reduce_ms.append(r_ms)
+        kernel_ms = sum(reduce_ms) / len(reduce_ms)
+        algorithmic = workloads.segreduce_bytes(COUNT, NUM_SEGMENTS, 4)
+        peak, peak_kind = measured_peak()
+        achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
+        roofline = {
+            "bound": "hbm", "kernel": "segreduce_k",
+            "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": "of " + peak_kind,
+            "algorithmic_bytes": algorithmic,
+            "traffic": algorithmic * TRAFFIC_PER_ALGORITHMIC_BYTE,
+            "kernel_ms": kernel_ms,
+            "partition_kernel_ms": sum(part_ms) / len(part_ms),
+        }
+    clocks = sampler.stop() if sampler else None
+
+    # End to end through the host-buffer entry point of the C ABI.
+    hv = values.cpu().pin_memory()
+    hs = (table if world > 1 else seg).cpu().pin_memory()
+    ho = torch.empty(hs.numel(), dtype=torch.float32).pin_memory()
+    e2e_steps = max(2, min(args.steps, 5))
+    for _ in range(2):
+        mgpu.segreduce_host(hv, hs, op="plus", init=0.0, out=ho)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        mgpu.segreduce_host(hv, hs, op="plus", init=0.0, out=ho)
+        if world > 1:
+            # Boundary records cross through a 16-byte device tensor.
+            rec = torch.from_numpy(sharded.pack_record_host(
+                int(ho[:1].view(torch.int32).item()) & 0xffffffff,
+                hs.numpy(), COUNT).view("int64").copy()).to(device)
+            gathered = torch.empty(world * 2, dtype=torch.int64, device=device)
+            dist.all_gather_into_tensor(gathered, rec)
+            recs = gathered.cpu().numpy().view("uint64").reshape(world, 2)
+            flags = [int(f) for f in recs[:, 1]]
+            for k in sharded.fold_plan(flags, rank):
+                part = recs[k, :1].view("float32")[0]
+                ho[-1] = part if flags[rank] & sharded.LAST_EMPTY \
+                    else ho[-1] + part
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = {"value": world * COUNT / e2e_s / 1e9, "unit": UNIT,
+           "h2d_bytes_per_step": hv.numel() * 4 + hs.numel() * 4,
+           "d2h_bytes_per_step": ho.numel() * 4,
+           "ms_per_step": e2e_s * 1e3, "steps": e2e_steps,
+           "api": "mgpu_b200_segreduce_host (pinned host buffers)"}
+
+    if rank == 0:
+        cpu = None
+        if world == 1:
+            import oracle
+            cv, cs = cpu_sample()
+            threads = oracle.max_threads()
+            cpu_value, reps, spent = time_cpu(cv, cs, 10.0, threads)
+            cpu = {"value": cpu_value, "unit": UNIT, "cores": threads,
+                   "kind": "port",
+                   "sample": "%d repetitions (%.1f s) of the host loop of "
+                             "tests/test_segreduce.cu:40-49 (C port, OpenMP "
+                             "over segments) on a %d-item / %d-segment sample "
+                             "of the workload" % (reps, spent, cv.size, cs.size)}
+        launches_per_step = 2 if world == 1 else 4
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(world),
+            "hbm_gbs_per_gpu": workloads.segreduce_bytes(
+                COUNT, NUM_SEGMENTS, 4) / (ms_per_step * 1e-3) / 1e9,
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": launches_per_step * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours",
+                        choices=["ours", "reference", "reference-cuda"])
+    args = parser.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_cpu(args, rank, world)
+    elif args.impl == "reference-cuda":
+        run_reference_cuda(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -706,11 +706,13 @@ constexpr uint64_t default_timeout_ns = 2000000000ull;
 
 // Enqueue partitioner + reduction on `stream`. `workspace` must hold
 // segreduce_plan_t<...>(count, num_segments).bytes bytes, 128-byte aligned.
+// `after_partition`, when given, is recorded between the two kernels.
 template<typename tuning_t, typename type_t, typename source_t,
   typename segments_it, typename output_it, typename op_t>
 void segreduce_enqueue(source_t source, int count, segments_it segments,
   int num_segments, output_it output, op_t op, type_t init, void* workspace,
-  cudaStream_t stream, uint64_t timeout_ns = default_timeout_ns) {
+  cudaStream_t stream, uint64_t timeout_ns = default_timeout_ns,
+  cudaEvent_t after_partition = nullptr) {
 
   typedef segreduce_smem_t<tuning_t, type_t> layout_t;
   typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t>
@@ -727,6 +729,7 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
     (int64_t)tuning_t::nv, plan.num_tiles + 1, partitions, stream,
     header, 32, (uint32_t*)state,
     (int)tile_state_traits<type_t>::clear_words);
+  if(after_partition) cudaEventRecord(after_partition, stream);
 
   auto kernel = segreduce_k<tuning_t, type_t, source_t, segments_it,
     output_it, op_t>;

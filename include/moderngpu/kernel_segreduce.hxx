@@ -2,3 +2,4 @@
 // the implementation lives under b200/.
 #pragma once
 #include "b200/segreduce.hxx"
+#include "b200/lbs_segreduce.hxx"

@@ -77,6 +77,20 @@ int mgpu_b200_segreduce(int dtype, int op, const void* input_device, int count,
   void* stream);
 
 /*
+ * Diagnostic form of mgpu_b200_segreduce: same arguments and result, but the
+ * call waits for the device and reports how long its two kernels ran, as
+ * measured by CUDA events on `stream`: the merge-path partitioner
+ * (*partition_ms) and the reduction kernel (*reduce_ms). No counterpart in
+ * the reference; it exists so that a benchmark can attribute time to the
+ * dominant kernel. Either pointer may be NULL. Not safe to call from two
+ * host threads at once.
+ */
+int mgpu_b200_segreduce_profile(int dtype, int op, const void* input_device,
+  int count, const int* segments_device, int num_segments, void* output_device,
+  const void* init_host, void* workspace_device, size_t workspace_bytes,
+  void* stream, float* partition_ms, float* reduce_ms);
+
+/*
  * Reads back the status word of the most recent call that used `workspace`
  * (waits for `stream`). *status receives MGPU_B200_STATUS_*; the return value
  * is MGPU_B200_E_DEVICE_STATUS when it is not MGPU_B200_STATUS_OK.
@@ -93,6 +107,92 @@ int mgpu_b200_workspace_status(const void* workspace_device, void* stream,
  */
 int mgpu_b200_load_balance_partitions(int count, const int* segments_device,
   int num_segments, int spacing, int* partitions_device, void* stream);
+
+/*
+ * mgpu::spmv (reference: src/moderngpu/kernel_segreduce.hxx:285-298):
+ *   y[r] = sum over the non-zeros i of row r of matrix[i] * vector[columns[i]]
+ * for a CSR matrix with nnz non-zeros and `rows` rows; row_starts plays the
+ * part of `segments` (first non-zero of each row), rows without non-zeros
+ * give 0. dtype is MGPU_B200_F32 or MGPU_B200_F64; columns are int32 and are
+ * not range-checked. Workspace as for mgpu_b200_segreduce.
+ */
+size_t mgpu_b200_spmv_workspace_bytes(int dtype, int nnz, int rows);
+
+int mgpu_b200_spmv(int dtype, const void* matrix_device,
+  const int* columns_device, const void* vector_device, int nnz,
+  const int* row_starts_device, int rows, void* y_device,
+  void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
+ * mgpu::transform_lbs (reference: src/moderngpu/kernel_load_balance.hxx:8-76)
+ * with the functor that records its arguments: for every item index in
+ * [0, count), seg_out[index] = (number of segment starts <= index) - 1 and,
+ * when rank_out is not NULL, rank_out[index] = index - segments[seg].
+ * With rank_out == NULL this is mgpu::load_balance_search (:78-86).
+ * Workspace: mgpu_b200_lbs_workspace_bytes(count, num_segments) bytes,
+ * 128-byte aligned, contents overwritten.
+ */
+size_t mgpu_b200_lbs_workspace_bytes(int count, int num_segments);
+
+int mgpu_b200_load_balance_search(int count, const int* segments_device,
+  int num_segments, int* seg_out_device, int* rank_out_device,
+  void* workspace_device, size_t workspace_bytes, void* stream);
+
+/*
+ * mgpu::interval_expand (reference: src/moderngpu/kernel_intervalmove.hxx:
+ * 7-20): output[index] = input[segment of index], elements of elem_bytes
+ * bytes (1, 2, 4 or 8) copied bit for bit. Workspace as for
+ * mgpu_b200_load_balance_search.
+ */
+int mgpu_b200_interval_expand(int elem_bytes, const void* input_device,
+  int count, const int* segments_device, int num_segments,
+  void* output_device, void* workspace_device, size_t workspace_bytes,
+  void* stream);
+
+/*
+ * mgpu::segreduce on HOST arrays: what a caller of the reference does with
+ * to_mem / segreduce / from_mem (reference: src/moderngpu/memory.hxx:61-75,
+ * tests/test_segreduce.cu:24-38), as one call. input, segments and output
+ * are host pointers (pinned memory copies fastest). The call cuts the problem
+ * at segment boundaries into chunks of about 32 Mi items and overlaps the
+ * copy-in, the reduction and the copy-out of successive chunks on three
+ * internal streams of the current device; it returns when output_host holds
+ * every result. Device buffers are kept and reused by later calls.
+ * `reserved` must be NULL.
+ */
+int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
+  int count, const int* segments_host, int num_segments, void* output_host,
+  const void* init_host, void* reserved);
+
+/*
+ * Multi-GPU layer (no counterpart in the reference, which is single-device).
+ * The item range of a large problem is cut across GPUs; GPU r holds count_r
+ * items and a shard-local start table `starts` whose entry 0 is always 0 and
+ * stands for the segment carried in from the left, followed by the local
+ * offsets of the segments that START inside the shard. Each GPU runs
+ * mgpu_b200_segreduce on (items, starts): out[0] is then its boundary
+ * partial, out[1..] its own segments, the last of which may continue on later
+ * GPUs.
+ *
+ * mgpu_b200_shard_pack writes one 16-byte record {value bits, flags} that
+ * describes the shard's boundary: what out[0] holds and whether the shard
+ * contains a segment start. The caller exchanges the records of all GPUs
+ * (16 bytes per GPU: an all-gather, or peer-to-peer copies into every GPU's
+ * own memory) into `records_device`, ordered by shard.
+ *
+ * mgpu_b200_shard_fold then makes the GPU that owns a straddling segment fold
+ * in the partials of the following shards, in shard order:
+ *   out[num_starts - 1] = op(out[num_starts - 1], partial_{r+1}, ...)
+ * up to and including the first later shard that holds a start of its own.
+ * `init_host` is the same init that the reduction used.
+ */
+int mgpu_b200_shard_pack(int dtype, const void* out_device,
+  const int* starts_device, int num_starts, int count, void* record_device,
+  void* stream);
+
+int mgpu_b200_shard_fold(int dtype, int op, const void* records_device,
+  int rank, int world, void* out_device, int num_starts,
+  const void* init_host, void* stream);
 
 #ifdef __cplusplus
 }

@@ -17,6 +17,7 @@ from .binding import (  # noqa: F401
     load_library,
     segreduce,
     segreduce_host,
+    segreduce_profile,
     spmv,
     transform_lbs,
     workspace_status,
@@ -25,5 +26,5 @@ from .binding import (  # noqa: F401
 __all__ = [
     "LibraryMissing", "MgpuError", "interval_expand", "lib_path",
     "load_balance_partitions", "load_balance_search", "load_library",
-    "segreduce", "segreduce_host", "spmv", "transform_lbs", "workspace_status",
+    "segreduce", "segreduce_host", "segreduce_profile", "spmv", "transform_lbs", "workspace_status",
 ]

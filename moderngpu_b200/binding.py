@@ -64,6 +64,11 @@ def load_library():
     lib.mgpu_b200_segreduce.argtypes = [
         c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
         c_void_p, c_size_t, c_void_p]
+    lib.mgpu_b200_segreduce_profile.restype = c_int
+    lib.mgpu_b200_segreduce_profile.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_void_p, c_size_t, c_void_p, ctypes.POINTER(ctypes.c_float),
+        ctypes.POINTER(ctypes.c_float)]
     lib.mgpu_b200_workspace_status.restype = c_int
     lib.mgpu_b200_workspace_status.argtypes = [
         c_void_p, c_void_p, ctypes.POINTER(c_int)]
@@ -94,6 +99,13 @@ def _declare_optional(lib):
     lib.mgpu_b200_interval_expand.restype = c_int
     lib.mgpu_b200_interval_expand.argtypes = [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_size_t,
+        c_void_p]
+    lib.mgpu_b200_shard_pack.restype = c_int
+    lib.mgpu_b200_shard_pack.argtypes = [
+        c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lib.mgpu_b200_shard_fold.restype = c_int
+    lib.mgpu_b200_shard_fold.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
         c_void_p]
     lib.mgpu_b200_segreduce_host.restype = c_int
     lib.mgpu_b200_segreduce_host.argtypes = [
@@ -164,6 +176,31 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
             num_segments, out.data_ptr(), ctypes.byref(init_c),
             workspace.data_ptr(), workspace.numel(), _stream(input.device)))
     return out
+
+
+def segreduce_profile(input, segments, op="plus", init=0, out=None,
+                      workspace=None):
+    """segreduce that waits for the device and returns
+    (out, partition_ms, reduce_ms): the device time of its two kernels."""
+    lib = load_library()
+    _require_cuda(input, "input")
+    _require_cuda(segments, "segments", torch.int32)
+    count, num_segments = input.numel(), segments.numel()
+    if out is None:
+        out = torch.empty(num_segments, dtype=input.dtype, device=input.device)
+    dtype = _DTYPES[input.dtype]
+    need = lib.mgpu_b200_segreduce_workspace_bytes(dtype, count, num_segments)
+    if workspace is None:
+        workspace = _workspace(input.device, need)
+    init_c = _CTYPES[input.dtype](init)
+    part, red = ctypes.c_float(0), ctypes.c_float(0)
+    with torch.cuda.device(input.device):
+        _check(lib.mgpu_b200_segreduce_profile(
+            dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
+            num_segments, out.data_ptr(), ctypes.byref(init_c),
+            workspace.data_ptr(), workspace.numel(), _stream(input.device),
+            ctypes.byref(part), ctypes.byref(red)))
+    return out, part.value, red.value
 
 
 def workspace_status(workspace=None, device=None):

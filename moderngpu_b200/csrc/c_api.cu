@@ -2,6 +2,11 @@
 // include/moderngpu/. Declarations and contracts: include/moderngpu_b200.h.
 #include <moderngpu_b200.h>
 #include <moderngpu/kernel_segreduce.hxx>
+#include <moderngpu/kernel_load_balance.hxx>
+#include <moderngpu/kernel_intervalmove.hxx>
+#include <mutex>
+#include <vector>
+#include <algorithm>
 
 using namespace mgpu;
 
@@ -27,6 +32,10 @@ size_t segreduce_bytes(int count, int num_segments) {
   return plan.bytes;
 }
 
+// Event recorded between the partition kernel and the reduction kernel of the
+// next segreduce call (diagnostic entry point only).
+cudaEvent_t g_between = nullptr;
+
 template<typename type_t, typename op_t>
 int segreduce_typed(const void* input, int count, const int* segments,
   int num_segments, void* output, const void* init_host, void* workspace,
@@ -37,7 +46,8 @@ int segreduce_typed(const void* input, int count, const int* segments,
   detail::array_source_t<type_t> source { (const type_t*)input };
   try {
     detail::segreduce_enqueue<tuning_t>(source, count, segments, num_segments,
-      (type_t*)output, op_t(), init, workspace, stream, g_timeout_ns);
+      (type_t*)output, op_t(), init, workspace, stream, g_timeout_ns,
+      g_between);
   } catch(cuda_exception_t& e) {
     return cuda_code(e.result);
   }
@@ -61,6 +71,208 @@ int segreduce_op(int op, const void* input, int count, const int* segments,
   }
   return MGPU_B200_E_UNSUPPORTED;
 }
+
+////////////////////////////////////////////////////////////////////////////////
+// spmv: products matrix[i] * x[columns[i]] evaluated by the reduction kernel's
+// consumer threads (reference: src/moderngpu/kernel_segreduce.hxx:285-298).
+
+template<typename type_t>
+struct spmv_product_t {
+  const type_t* matrix;
+  const int* columns;
+  const type_t* x;
+  typedef type_t value_type;
+  MGPU_DEVICE type_t operator[](int index) const {
+    return matrix[index] * __ldg(x + columns[index]);
+  }
+};
+
+template<typename type_t>
+int spmv_typed(const void* matrix, const int* columns, const void* x, int nnz,
+  const int* row_starts, int rows, void* y, void* workspace,
+  cudaStream_t stream) {
+  typedef typename type_tuning<type_t>::type tuning_t;
+  typedef spmv_product_t<type_t> product_t;
+  detail::iterator_source_t<product_t, type_t> source {
+    product_t { (const type_t*)matrix, columns, (const type_t*)x } };
+  try {
+    detail::segreduce_enqueue<tuning_t>(source, nnz, row_starts, rows,
+      (type_t*)y, plus_t<type_t>(), (type_t)0, workspace, stream,
+      g_timeout_ns);
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
+  }
+  return last_launch_code();
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// Load-balancing search functors.
+
+struct store_seg_rank_t {
+  int* seg_out;
+  int* rank_out;
+  MGPU_DEVICE void operator()(int index, int seg, int rank, tuple<>) const {
+    seg_out[index] = seg;
+    if(rank_out) rank_out[index] = rank;
+  }
+};
+
+template<typename elem_t>
+struct expand_t {
+  elem_t* output;
+  MGPU_DEVICE void operator()(int index, int seg, int rank,
+    tuple<elem_t> value) const {
+    output[index] = get<0>(value);
+  }
+};
+
+typedef detail::lbs_default_tuning lbs_tuning;
+
+template<typename elem_t>
+int expand_typed(const void* input, int count, const int* segments,
+  int num_segments, void* output, void* workspace, cudaStream_t stream) {
+  uint32_t* status = (uint32_t*)workspace + 1;
+  int* partitions = (int*)((char*)workspace + 128);
+  cudaMemsetAsync(workspace, 0, 128, stream);
+  detail::transform_lbs_enqueue<lbs_tuning>(
+    expand_t<elem_t> { (elem_t*)output }, count, segments, num_segments,
+    make_tuple((const elem_t*)input), partitions, stream, g_timeout_ns,
+    status);
+  return last_launch_code();
+}
+
+inline size_t lbs_bytes(int count, int num_segments) {
+  return 128 + (detail::lbs_partition_bytes(count, num_segments,
+    lbs_tuning::nv) + 127) / 128 * 128;
+}
+
+////////////////////////////////////////////////////////////////////////////////
+// Host-buffer segreduce: the arrays live in host memory; the call cuts the
+// problem at segment boundaries into chunks, and pipelines
+// copy-in / reduce / copy-out of successive chunks over three streams.
+
+template<typename type_t>
+__global__ void rebase_offsets_k(int* offsets, int n, int base) {
+  int i = (int)(blockIdx.x * blockDim.x + threadIdx.x);
+  if(i < n) offsets[i] -= base;
+}
+
+struct host_slot_t {
+  cudaStream_t stream = nullptr;
+  void* items = nullptr;
+  int* offsets = nullptr;
+  void* output = nullptr;
+  void* workspace = nullptr;
+  size_t items_cap = 0, offsets_cap = 0, output_cap = 0, workspace_cap = 0;
+};
+
+struct host_pipeline_t {
+  enum { slots = 3 };
+  host_slot_t slot[slots];
+  int device = -1;
+};
+
+std::mutex g_host_mutex;
+host_pipeline_t g_host_pipeline[16];
+
+cudaError_t grow(void** p, size_t* cap, size_t need) {
+  if(*cap >= need) return cudaSuccess;
+  if(*p) cudaFree(*p);
+  *p = nullptr;
+  *cap = 0;
+  size_t want = need + need / 4 + 256;
+  cudaError_t e = cudaMalloc(p, want);
+  if(cudaSuccess == e) *cap = want;
+  return e;
+}
+
+int segreduce_dispatch(int dtype, int op, const void* input, int count,
+  const int* segments, int num_segments, void* output, const void* init_host,
+  void* workspace, cudaStream_t stream);
+
+size_t elem_size(int dtype) {
+  switch(dtype) {
+    case MGPU_B200_F32: case MGPU_B200_I32: return 4;
+    case MGPU_B200_F64: case MGPU_B200_I64: return 8;
+  }
+  return 0;
+}
+
+int segreduce_host_impl(int dtype, int op, const char* input, int count,
+  const int* segments, int num_segments, char* output,
+  const void* init_host) {
+  const size_t es = elem_size(dtype);
+  if(!es) return MGPU_B200_E_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_host_mutex);
+
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if(cudaSuccess != e) return cuda_code(e);
+  if(device < 0 || device >= 16) return MGPU_B200_E_UNSUPPORTED;
+  host_pipeline_t& pipe = g_host_pipeline[device];
+  if(pipe.device != device) {
+    for(auto& s : pipe.slot) {
+      e = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking);
+      if(cudaSuccess != e) return cuda_code(e);
+    }
+    pipe.device = device;
+  }
+
+  // Chunks of about 32 Mi items, cut where a segment starts.
+  const int target = 32 << 20;
+  std::vector<int> cut;        // first segment of each chunk, then the end
+  cut.push_back(0);
+  while(cut.back() < num_segments) {
+    int s0 = cut.back();
+    int64_t want = (int64_t)segments[s0] + target;
+    const int* hit = std::lower_bound(segments + s0 + 1,
+      segments + num_segments, want > count ? count : (int)want);
+    int s1 = (int)(hit - segments);
+    if(s1 <= s0) s1 = s0 + 1;
+    // Keep trailing empty segments at the array's end in the last chunk.
+    if(want >= count) s1 = num_segments;
+    cut.push_back(s1);
+  }
+
+  int code = MGPU_B200_OK;
+  for(size_t c = 0; c + 1 < cut.size() && MGPU_B200_OK == code; ++c) {
+    host_slot_t& s = pipe.slot[c % host_pipeline_t::slots];
+    int s0 = cut[c], s1 = cut[c + 1];
+    int item0 = segments[s0];
+    int item1 = s1 < num_segments ? segments[s1] : count;
+    int n_items = item1 - item0, n_segs = s1 - s0;
+    size_t ws_need = mgpu_b200_segreduce_workspace_bytes(dtype, n_items,
+      n_segs);
+    // The slot's previous chunk must be finished before its buffers change.
+    e = cudaStreamSynchronize(s.stream);
+    if(cudaSuccess == e) e = grow(&s.items, &s.items_cap, (size_t)n_items * es + 64);
+    if(cudaSuccess == e) e = grow((void**)&s.offsets, &s.offsets_cap, (size_t)n_segs * 4 + 64);
+    if(cudaSuccess == e) e = grow(&s.output, &s.output_cap, (size_t)n_segs * es + 64);
+    if(cudaSuccess == e) e = grow(&s.workspace, &s.workspace_cap, ws_need + 256);
+    if(cudaSuccess == e && n_items)
+      e = cudaMemcpyAsync(s.items, input + (size_t)item0 * es,
+        (size_t)n_items * es, cudaMemcpyHostToDevice, s.stream);
+    if(cudaSuccess == e)
+      e = cudaMemcpyAsync(s.offsets, segments + s0, (size_t)n_segs * 4,
+        cudaMemcpyHostToDevice, s.stream);
+    if(cudaSuccess != e) { code = cuda_code(e); break; }
+    if(item0)
+      rebase_offsets_k<int><<<div_up(n_segs, 256), 256, 0, s.stream>>>(
+        s.offsets, n_segs, item0);
+    code = segreduce_dispatch(dtype, op, s.items, n_items, s.offsets, n_segs,
+      s.output, init_host, s.workspace, s.stream);
+    if(MGPU_B200_OK != code) break;
+    e = cudaMemcpyAsync(output + (size_t)s0 * es, s.output,
+      (size_t)n_segs * es, cudaMemcpyDeviceToHost, s.stream);
+    if(cudaSuccess != e) code = cuda_code(e);
+  }
+  for(auto& s : pipe.slot) {
+    e = cudaStreamSynchronize(s.stream);
+    if(cudaSuccess != e && MGPU_B200_OK == code) code = cuda_code(e);
+  }
+  return code;
+}
+
 
 inline bool sizes_ok(int count, int num_segments) {
   return count >= 0 && num_segments >= 0 &&
@@ -121,22 +333,39 @@ int mgpu_b200_segreduce(int dtype, int op, const void* input_device, int count,
   if(!need) return MGPU_B200_E_UNSUPPORTED;
   if(workspace_bytes < need) return MGPU_B200_E_WORKSPACE;
 
+  return segreduce_dispatch(dtype, op, input_device, count, segments_device,
+    num_segments, output_device, init_host, workspace_device,
+    (cudaStream_t)stream);
+}
+
+int mgpu_b200_segreduce_profile(int dtype, int op, const void* input_device,
+  int count, const int* segments_device, int num_segments, void* output_device,
+  const void* init_host, void* workspace_device, size_t workspace_bytes,
+  void* stream, float* partition_ms, float* reduce_ms) {
   cudaStream_t s = (cudaStream_t)stream;
-  switch(dtype) {
-    case MGPU_B200_F32:
-      return segreduce_op<float>(op, input_device, count, segments_device,
-        num_segments, output_device, init_host, workspace_device, s);
-    case MGPU_B200_F64:
-      return segreduce_op<double>(op, input_device, count, segments_device,
-        num_segments, output_device, init_host, workspace_device, s);
-    case MGPU_B200_I32:
-      return segreduce_op<int32_t>(op, input_device, count, segments_device,
-        num_segments, output_device, init_host, workspace_device, s);
-    case MGPU_B200_I64:
-      return segreduce_op<int64_t>(op, input_device, count, segments_device,
-        num_segments, output_device, init_host, workspace_device, s);
+  cudaEvent_t ev[3];
+  for(auto& e : ev) {
+    cudaError_t c = cudaEventCreate(&e);
+    if(cudaSuccess != c) return cuda_code(c);
   }
-  return MGPU_B200_E_UNSUPPORTED;
+  cudaEventRecord(ev[0], s);
+  g_between = ev[1];
+  int code = mgpu_b200_segreduce(dtype, op, input_device, count,
+    segments_device, num_segments, output_device, init_host, workspace_device,
+    workspace_bytes, stream);
+  g_between = nullptr;
+  cudaEventRecord(ev[2], s);
+  cudaError_t c = cudaEventSynchronize(ev[2]);
+  if(MGPU_B200_OK == code && cudaSuccess != c) code = cuda_code(c);
+  if(MGPU_B200_OK == code) {
+    float a = 0, b = 0;
+    if(cudaSuccess != cudaEventElapsedTime(&a, ev[0], ev[1])) a = 0;
+    if(cudaSuccess != cudaEventElapsedTime(&b, ev[1], ev[2])) b = 0;
+    if(partition_ms) *partition_ms = a;
+    if(reduce_ms) *reduce_ms = b;
+  }
+  for(auto& e : ev) cudaEventDestroy(e);
+  return code;
 }
 
 int mgpu_b200_workspace_status(const void* workspace_device, void* stream,
@@ -162,6 +391,122 @@ int mgpu_b200_load_balance_partitions(int count, const int* segments_device,
     (int64_t)spacing, num_partitions, partitions_device,
     (cudaStream_t)stream);
   return last_launch_code();
+}
+
+} // extern "C"
+
+namespace {
+int segreduce_dispatch(int dtype, int op, const void* input, int count,
+  const int* segments, int num_segments, void* output, const void* init_host,
+  void* workspace, cudaStream_t s) {
+  switch(dtype) {
+    case MGPU_B200_F32:
+      return segreduce_op<float>(op, input, count, segments, num_segments,
+        output, init_host, workspace, s);
+    case MGPU_B200_F64:
+      return segreduce_op<double>(op, input, count, segments, num_segments,
+        output, init_host, workspace, s);
+    case MGPU_B200_I32:
+      return segreduce_op<int32_t>(op, input, count, segments, num_segments,
+        output, init_host, workspace, s);
+    case MGPU_B200_I64:
+      return segreduce_op<int64_t>(op, input, count, segments, num_segments,
+        output, init_host, workspace, s);
+  }
+  return MGPU_B200_E_UNSUPPORTED;
+}
+} // namespace
+
+extern "C" {
+
+size_t mgpu_b200_spmv_workspace_bytes(int dtype, int nnz, int rows) {
+  return mgpu_b200_segreduce_workspace_bytes(dtype, nnz, rows);
+}
+
+int mgpu_b200_spmv(int dtype, const void* matrix_device,
+  const int* columns_device, const void* vector_device, int nnz,
+  const int* row_starts_device, int rows, void* y_device,
+  void* workspace_device, size_t workspace_bytes, void* stream) {
+  if(!sizes_ok(nnz, rows)) return MGPU_B200_E_INVALID;
+  if(0 == nnz + rows) return MGPU_B200_OK;
+  if((nnz && (!matrix_device || !columns_device || !vector_device)) ||
+    (rows && (!row_starts_device || !y_device)) || !workspace_device ||
+    (uintptr_t)workspace_device % 128)
+    return MGPU_B200_E_INVALID;
+  if(MGPU_B200_F32 != dtype && MGPU_B200_F64 != dtype)
+    return MGPU_B200_E_UNSUPPORTED;
+  if(workspace_bytes < mgpu_b200_spmv_workspace_bytes(dtype, nnz, rows))
+    return MGPU_B200_E_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if(MGPU_B200_F32 == dtype)
+    return spmv_typed<float>(matrix_device, columns_device, vector_device,
+      nnz, row_starts_device, rows, y_device, workspace_device, s);
+  return spmv_typed<double>(matrix_device, columns_device, vector_device, nnz,
+    row_starts_device, rows, y_device, workspace_device, s);
+}
+
+size_t mgpu_b200_lbs_workspace_bytes(int count, int num_segments) {
+  if(!sizes_ok(count, num_segments)) return 0;
+  return lbs_bytes(count, num_segments);
+}
+
+int mgpu_b200_load_balance_search(int count, const int* segments_device,
+  int num_segments, int* seg_out_device, int* rank_out_device,
+  void* workspace_device, size_t workspace_bytes, void* stream) {
+  if(!sizes_ok(count, num_segments)) return MGPU_B200_E_INVALID;
+  if(0 == count + num_segments) return MGPU_B200_OK;
+  if((count && !seg_out_device) || (num_segments && !segments_device) ||
+    !workspace_device || (uintptr_t)workspace_device % 128)
+    return MGPU_B200_E_INVALID;
+  if(workspace_bytes < lbs_bytes(count, num_segments))
+    return MGPU_B200_E_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  uint32_t* status = (uint32_t*)workspace_device + 1;
+  int* partitions = (int*)((char*)workspace_device + 128);
+  cudaMemsetAsync(workspace_device, 0, 128, s);
+  detail::transform_lbs_enqueue<lbs_tuning>(
+    store_seg_rank_t { seg_out_device, rank_out_device }, count,
+    segments_device, num_segments, tuple<>(), partitions, s, g_timeout_ns,
+    status);
+  return last_launch_code();
+}
+
+int mgpu_b200_interval_expand(int elem_bytes, const void* input_device,
+  int count, const int* segments_device, int num_segments,
+  void* output_device, void* workspace_device, size_t workspace_bytes,
+  void* stream) {
+  if(!sizes_ok(count, num_segments)) return MGPU_B200_E_INVALID;
+  if(0 == count + num_segments) return MGPU_B200_OK;
+  if((count && !output_device) ||
+    (num_segments && (!segments_device || !input_device)) ||
+    !workspace_device || (uintptr_t)workspace_device % 128)
+    return MGPU_B200_E_INVALID;
+  if(workspace_bytes < lbs_bytes(count, num_segments))
+    return MGPU_B200_E_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch(elem_bytes) {
+    case 1: return expand_typed<uint8_t>(input_device, count, segments_device,
+      num_segments, output_device, workspace_device, s);
+    case 2: return expand_typed<uint16_t>(input_device, count, segments_device,
+      num_segments, output_device, workspace_device, s);
+    case 4: return expand_typed<uint32_t>(input_device, count, segments_device,
+      num_segments, output_device, workspace_device, s);
+    case 8: return expand_typed<uint64_t>(input_device, count, segments_device,
+      num_segments, output_device, workspace_device, s);
+  }
+  return MGPU_B200_E_UNSUPPORTED;
+}
+
+int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
+  int count, const int* segments_host, int num_segments, void* output_host,
+  const void* init_host, void* reserved) {
+  (void)reserved;
+  if(!sizes_ok(count, num_segments) || !init_host) return MGPU_B200_E_INVALID;
+  if(0 == num_segments) return MGPU_B200_OK;
+  if((count && !input_host) || !segments_host || !output_host)
+    return MGPU_B200_E_INVALID;
+  return segreduce_host_impl(dtype, op, (const char*)input_host, count,
+    segments_host, num_segments, (char*)output_host, init_host);
 }
 
 } // extern "C"

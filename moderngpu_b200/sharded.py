@@ -1,0 +1,165 @@
+"""Multi-GPU segmented reduction: one process per GPU, the item range cut
+evenly across ranks, one 16-byte boundary record exchanged per rank.
+
+The reference is single-device (src/moderngpu/context.hxx:85,109-110 knows one
+stream on the current device); this layer is new. Data path per rank:
+
+  1. mgpu_b200_segreduce on the shard (items, shard-local start table);
+  2. mgpu_b200_shard_pack: boundary partial + flags -> 16-byte record;
+  3. torch.distributed all_gather of the records (16 bytes per rank -- the
+     only exchange; NVLink carries it when the backend is NCCL);
+  4. mgpu_b200_shard_fold: the rank that owns a straddling segment folds the
+     following ranks' partials into its last output, in rank order.
+
+Shard-local start table: entry 0 is always 0 and stands for the segment
+carried in from the previous rank; the remaining entries are the local offsets
+of the segments that START inside the shard. `shard_table` derives it from a
+global start table.
+"""
+import ctypes
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import binding
+
+RECORD_BYTES = 16
+HAS_PARTIAL, HAS_START, LAST_EMPTY = 1, 2, 4
+
+
+def shard_bounds(count, world):
+    """Item range [begin, end) of every rank: an even cut of [0, count)."""
+    edges = [(count * r) // world for r in range(world + 1)]
+    return [(edges[r], edges[r + 1]) for r in range(world)]
+
+
+def shard_table(segments, count, rank, world):
+    """Shard-local start table of `rank` for a global problem.
+
+    segments: global int64/int32 start offsets (numpy, sorted, segments[0]==0).
+    Returns (item_begin, item_end, first_segment, table) where `table` is an
+    int32 array [0, local starts...] and `first_segment` is the global index
+    of the first segment that starts inside the shard. A segment that starts
+    exactly at item_end belongs to the next rank, except on the last rank,
+    which also takes the trailing (empty) segments that start at count."""
+    segments = np.asarray(segments)
+    begin, end = shard_bounds(count, world)[rank]
+    first = int(np.searchsorted(segments, begin, side="left"))
+    if rank == world - 1:
+        last = segments.size
+    else:
+        last = int(np.searchsorted(segments, end, side="left"))
+    local = (segments[first:last].astype(np.int64) - begin).astype(np.int32)
+    table = np.concatenate([np.zeros(1, dtype=np.int32), local])
+    return begin, end, first, table
+
+
+def pack_record_host(out0_bits, table, count):
+    """Host mirror of mgpu_b200_shard_pack (used on CPU ranks in tests)."""
+    flags = 0
+    real = table.size > 1
+    first = int(table[1]) if real else count
+    if first > 0:
+        flags |= HAS_PARTIAL
+    if real:
+        flags |= HAS_START
+    if real and int(table[-1]) >= count:
+        flags |= LAST_EMPTY
+    rec = np.zeros(2, dtype=np.uint64)
+    rec[0] = out0_bits
+    rec[1] = flags
+    return rec
+
+
+def fold_plan(flags, rank):
+    """Ranks whose boundary partial the rank `rank` must fold into its last
+    segment, in order: every later rank with a partial, up to and including
+    the first later rank that holds a segment start of its own. Empty when
+    `rank` holds no segment start (it owns nothing)."""
+    if not flags[rank] & HAS_START:
+        return []
+    take = []
+    for k in range(rank + 1, len(flags)):
+        if flags[k] & HAS_PARTIAL:
+            take.append(k)
+        if flags[k] & HAS_START:
+            break
+    return take
+
+
+_NP_OPS = {"plus": lambda a, b: a + b, "max": max, "min": min}
+
+
+def sharded_segreduce(values, table, op="plus", init=0, group=None,
+                      local_reduce=None, records=None):
+    """Reduce this rank's shard and fold boundary partials across ranks.
+
+    values: this rank's items; table: its shard-local start table (see module
+    docstring). Returns the local outputs (table.numel() entries; entry 0 is
+    this rank's boundary partial, owned by an earlier rank).
+
+    On CUDA tensors every step runs in the library's kernels and the exchange
+    is one all_gather of 16 bytes per rank. `local_reduce`, given only by the
+    CPU tests of the host logic, replaces step 1 for CPU tensors; the record
+    packing and the fold then run in their host mirrors."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if values.is_cuda:
+        return _sharded_cuda(values, table, op, init, group, rank, world,
+                             records)
+    if local_reduce is None:
+        raise binding.LibraryMissing(
+            "sharded_segreduce runs on CUDA tensors only (no CPU fallback)")
+    return _sharded_host(values, table, op, init, group, rank, world,
+                         local_reduce)
+
+
+def _sharded_cuda(values, table, op, init, group, rank, world, records):
+    lib = binding.load_library()
+    dev = values.device
+    out = binding.segreduce(values, table, op=op, init=init)
+    dtype = binding._DTYPES[values.dtype]
+    stream = binding._stream(dev)
+    mine = torch.empty(RECORD_BYTES, dtype=torch.uint8, device=dev)
+    if records is None:
+        records = torch.empty(world * RECORD_BYTES, dtype=torch.uint8,
+                              device=dev)
+    with torch.cuda.device(dev):
+        binding._check(lib.mgpu_b200_shard_pack(
+            dtype, out.data_ptr(), table.data_ptr(), table.numel(),
+            values.numel(), mine.data_ptr(), stream))
+        if world > 1:
+            dist.all_gather_into_tensor(records, mine, group=group)
+        else:
+            records[:RECORD_BYTES].copy_(mine)
+        init_c = binding._CTYPES[values.dtype](init)
+        binding._check(lib.mgpu_b200_shard_fold(
+            dtype, binding._OPS[op], records.data_ptr(), rank, world,
+            out.data_ptr(), table.numel(), ctypes.byref(init_c), stream))
+    return out
+
+
+def _sharded_host(values, table, op, init, group, rank, world, local_reduce):
+    v = values.numpy()
+    t = table.numpy()
+    out = np.array(local_reduce(v, t, op, init))
+    bits = np.zeros(1, dtype=np.uint64)
+    bits.view(np.uint8)[:out.itemsize] = out[:1].view(np.uint8)
+    rec = pack_record_host(bits[0], t, v.size)
+    mine = torch.from_numpy(rec.view(np.int64).copy())
+    gathered = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(gathered, mine, group=group)
+    recs = np.stack([g.numpy().view(np.uint64) for g in gathered])
+    flags = [int(f) for f in recs[:, 1]]
+    fold = _NP_OPS[op]
+    acc = None
+    for k in fold_plan(flags, rank):
+        val = recs[k, :1].view(np.uint8)[:out.itemsize].view(out.dtype)[0]
+        acc = val if acc is None else fold(acc, val)
+    if acc is not None:
+        if flags[rank] & LAST_EMPTY:
+            out[-1] = acc
+        else:
+            out[-1] = fold(out[-1], acc)
+    return torch.from_numpy(out)

@@ -1,0 +1,120 @@
+"""Load-balancing search, partitions and interval_expand: bit-exact against the
+CPU oracle and the golden vectors made by the reference's merge_path."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from moderngpu_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "lbs_partitions.json")
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def golden_cases():
+    with open(GOLDEN) as f:
+        return json.load(f)["cases"]
+
+
+@pytest.mark.parametrize("case", golden_cases(), ids=lambda c: c["name"])
+def test_partitions_match_golden(mgpu, case):
+    seg = dev(np.array(case["segments"], dtype=np.int32))
+    for spacing, expect in case["partitions"].items():
+        got = mgpu.load_balance_partitions(case["count"], seg, int(spacing))
+        assert got.cpu().tolist() == expect
+
+
+@pytest.mark.parametrize("count,num_segments,spacing", [
+    (1 << 20, 10_000, 896), (1 << 20, 10_001, 7160), (10_000_000, 10, 5112),
+    (5000, 200_000, 100), (5000, 200_003, 1), (100, 1, 7),
+])
+def test_partitions_match_oracle(mgpu, oracle, count, num_segments, spacing):
+    rng = np.random.default_rng(count % 1000 + num_segments)
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    got = mgpu.load_balance_partitions(count, dev(seg), spacing).cpu().numpy()
+    assert np.array_equal(got, oracle.load_balance_partitions(count, seg, spacing))
+
+
+def test_reference_lbs_test_shape(mgpu):
+    """tests/test_load_balance.cu:9-29: 200,030 items, segments of 100."""
+    count, spacing = 200_030, 100
+    seg = np.arange(0, count, spacing, dtype=np.int32)
+    got = mgpu.load_balance_search(count, dev(seg)).cpu().numpy()
+    assert np.array_equal(got, np.arange(count) // spacing)
+
+
+@pytest.mark.parametrize("count,num_segments", [
+    (10, 4), (1 << 20, 10_000), (3_000_001, 90_000), (5000, 200_000),
+    (4096, 1), (4097, 2), (1, 1),
+])
+def test_seg_and_rank_match_oracle(mgpu, oracle, count, num_segments):
+    rng = np.random.default_rng(count % 1000 + num_segments)
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    got_seg, got_rank = mgpu.transform_lbs(count, dev(seg))
+    want_seg, want_rank = oracle.load_balance_search(count, seg)
+    assert mgpu.workspace_status() == 0
+    assert np.array_equal(got_seg.cpu().numpy(), want_seg)
+    assert np.array_equal(got_rank.cpu().numpy(), want_rank)
+
+
+def test_unaligned_segments_pointer(mgpu, oracle):
+    rng = np.random.default_rng(3)
+    count, num_segments = 500_000, 7001
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    buf = torch.zeros(num_segments + 4, dtype=torch.int32, device="cuda")
+    view = buf[1:1 + num_segments]
+    view.copy_(torch.from_numpy(seg))
+    got_seg, got_rank = mgpu.transform_lbs(count, view)
+    want_seg, want_rank = oracle.load_balance_search(count, seg)
+    assert np.array_equal(got_seg.cpu().numpy(), want_seg)
+    assert np.array_equal(got_rank.cpu().numpy(), want_rank)
+
+
+@pytest.mark.parametrize("dtype", [torch.uint8, torch.int16, torch.float32,
+                                   torch.float64, torch.int64])
+def test_interval_expand(mgpu, oracle, dtype):
+    rng = np.random.default_rng(9)
+    count, num_segments = 1_000_000, 30_000
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    vals = torch.from_numpy(rng.integers(0, 120, size=num_segments)).to(dtype)
+    got = mgpu.interval_expand(vals.cuda(), count, dev(seg)).cpu().numpy()
+    want = oracle.interval_expand(vals.numpy(), count, seg)
+    assert np.array_equal(got, want)
+
+
+def test_config4_reduced(mgpu, oracle):
+    count, num_segments = 1 << 24, 1 << 18
+    seg = workloads.config4(seed=3, count=count, num_segments=num_segments)
+    got_seg, got_rank = mgpu.transform_lbs(count, seg)
+    want_seg, want_rank = oracle.load_balance_search(count, seg.cpu().numpy())
+    assert np.array_equal(got_seg.cpu().numpy(), want_seg)
+    assert np.array_equal(got_rank.cpu().numpy(), want_rank)
+
+
+def test_config4_full_size_properties(mgpu):
+    """268,435,456 items over 4,194,304 Pareto-sized segments, checked on the
+    device through properties that define the result uniquely:
+    seg is non-decreasing, segments[seg] <= index < segments[seg + 1], and
+    rank == index - segments[seg]."""
+    count = 1 << 28
+    seg = workloads.config4(seed=3)
+    ids, rank = mgpu.transform_lbs(count, seg)
+    assert mgpu.workspace_status() == 0
+    index = torch.arange(count, device="cuda", dtype=torch.int32)
+    starts = seg[ids.long()]
+    assert bool((rank == index - starts).all())
+    assert bool((rank >= 0).all())
+    ends = torch.cat([seg[1:], torch.tensor([count], device="cuda",
+                                            dtype=torch.int32)])[ids.long()]
+    assert bool((index < ends).all())
+    assert bool((ids[1:] >= ids[:-1]).all())

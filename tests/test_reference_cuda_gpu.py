@@ -1,0 +1,172 @@
+"""The reference's own CUDA build (oracle/_ref/libmgpu_ref.so: the unmodified
+moderngpu headers compiled for sm_100a) run on the same inputs as this
+library and as the CPU oracle. Pins the oracle to what the reference actually
+computes on a GPU, and checks the drop-in claim by running the reference's
+test programs compiled against this repository's headers.
+Skipped when the reference-derived binaries were not built."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+import torch
+
+from moderngpu_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+REF_LIB = os.path.join(REF_DIR, "libmgpu_ref.so")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not os.path.exists(REF_LIB):
+        pytest.skip("oracle/_ref/libmgpu_ref.so not built (make -C oracle ref)")
+    return ctypes.CDLL(REF_LIB)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def p(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def random_segments(rng, count, num_segments):
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    return seg
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_reference_segreduce_int_equals_oracle_and_ours(ref, mgpu, oracle, seed):
+    values, seg = workloads.config1(seed=seed)
+    v, s = dev(values), dev(seg)
+    out = torch.empty(seg.size, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert ref.ref_segreduce_i32(p(v), values.size, p(s), seg.size, p(out),
+                                 ctypes.c_int(-1), 0, 0, 1) == 0
+    want = oracle.segreduce(values, seg, init=-1)
+    assert np.array_equal(out.cpu().numpy(), want)
+    assert np.array_equal(mgpu.segreduce(v, s, init=-1).cpu().numpy(), want)
+
+
+def test_reference_own_test_workload(ref, oracle):
+    """transform_segreduce(index % 13), init -1, as tests/test_segreduce.cu."""
+    count, num_segments = 10_000_000, 10
+    seg = random_segments(np.random.default_rng(4), count, num_segments)
+    out = torch.empty(num_segments, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert ref.ref_transform_segreduce_index_mod(count, p(dev(seg)),
+                                                 num_segments, p(out), -1, 13) == 0
+    assert np.array_equal(out.cpu().numpy(),
+                          oracle.segreduce_index_mod(count, seg, -1, 13))
+
+
+def test_reference_max_and_fp_sum(ref, mgpu, oracle):
+    rng = np.random.default_rng(12)
+    count, num_segments = 2_000_000, 60_000
+    seg = random_segments(rng, count, num_segments)
+    values = (rng.random(count) * 2 - 1).astype(np.float32)
+    v, s = dev(values), dev(seg)
+    out = torch.empty(num_segments, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    assert ref.ref_segreduce_f32(p(v), count, p(s), num_segments, p(out),
+                                 ctypes.c_float(-5), 1, 0, 1) == 0
+    assert np.array_equal(out.cpu().numpy(),
+                          oracle.segreduce(values, seg, op="max", init=-5))
+    assert ref.ref_segreduce_f32(p(v), count, p(s), num_segments, p(out),
+                                 ctypes.c_float(0), 0, 0, 1) == 0
+    want, mags = oracle.segsum_wide(values, seg)
+    bound = 1e-5 * np.maximum(np.abs(want), mags)
+    assert np.all(np.abs(out.cpu().numpy() - want) <= bound)
+    ours = mgpu.segreduce(v, s, init=0.0).cpu().numpy()
+    assert np.all(np.abs(ours - want) <= bound)
+
+
+def test_reference_lbs_equals_oracle_and_ours(ref, mgpu, oracle):
+    rng = np.random.default_rng(13)
+    count, num_segments = 1_500_000, 40_000
+    seg = random_segments(rng, count, num_segments)
+    s = dev(seg)
+    ids = torch.empty(count, dtype=torch.int32, device="cuda")
+    rank = torch.empty(count, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert ref.ref_lbs_seg_rank(count, p(s), num_segments, p(ids), p(rank),
+                                0, 1) == 0
+    want_seg, want_rank = oracle.load_balance_search(count, seg)
+    assert np.array_equal(ids.cpu().numpy(), want_seg)
+    assert np.array_equal(rank.cpu().numpy(), want_rank)
+    got_seg, got_rank = mgpu.transform_lbs(count, s)
+    assert torch.equal(got_seg, ids) and torch.equal(got_rank, rank)
+
+
+def test_reference_partitions_and_expand(ref, mgpu, oracle):
+    rng = np.random.default_rng(14)
+    count, num_segments, spacing = 800_000, 9000, 896
+    seg = random_segments(rng, count, num_segments)
+    s = dev(seg)
+    n = (count + num_segments + spacing - 1) // spacing + 1
+    parts = torch.empty(n, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert ref.ref_load_balance_partitions(count, p(s), num_segments, spacing,
+                                           p(parts)) == 0
+    assert torch.equal(parts, mgpu.load_balance_partitions(count, s, spacing))
+    vals = dev(rng.integers(0, 1000, size=num_segments).astype(np.int32))
+    out = torch.empty(count, dtype=torch.int32, device="cuda")
+    assert ref.ref_interval_expand_i32(p(vals), count, p(s), num_segments,
+                                       p(out)) == 0
+    assert torch.equal(out, mgpu.interval_expand(vals, count, s))
+
+
+def test_reference_spmv_and_lbs_segreduce(ref, mgpu, oracle):
+    m, c, x, r = workloads.config3(seed=2, rows=1 << 16)
+    y = torch.empty(r.numel(), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    assert ref.ref_spmv_f32(p(m), p(c), p(x), m.numel(), p(r), r.numel(), p(y),
+                            0, 1) == 0
+    want, mags = oracle.spmv(m.cpu().numpy(), c.cpu().numpy(), x.cpu().numpy(),
+                             r.cpu().numpy())
+    bound = 1e-5 * np.maximum(np.abs(want), mags)
+    assert np.all(np.abs(y.cpu().numpy() - want) <= bound)
+    assert np.all(np.abs(mgpu.spmv(m, c, x, r).cpu().numpy() - want) <= bound)
+    # lbs_segreduce with f = seg + rank (tests/test_segreduce.cu:11-13).
+    seg = random_segments(np.random.default_rng(15), 500_000, 3000)
+    out = torch.empty(seg.size, dtype=torch.int32, device="cuda")
+    assert ref.ref_lbs_segreduce_seg_plus_rank(500_000, p(dev(seg)), seg.size,
+                                               p(out), -1) == 0
+    assert np.array_equal(out.cpu().numpy(),
+                          oracle.lbs_segreduce_seg_plus_rank(500_000, seg, -1))
+
+
+def test_dropin_load_balance_program():
+    """tests/test_load_balance.cu, unmodified, built on this repo's headers."""
+    exe = os.path.join(REF_DIR, "dropin_test_load_balance")
+    if not os.path.exists(exe):
+        pytest.skip("drop-in test binary not built")
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert run.returncode == 0
+    assert "ERROR AT" not in run.stdout
+    assert run.stdout.strip().splitlines()[-1].split(":")[0].strip() == "200029"
+
+
+def test_dropin_segreduce_program():
+    """tests/test_segreduce.cu, unmodified, built on this repo's headers. It
+    loops over 1000 seeds of 1e8 items with a serial host check, so it is cut
+    off after a while; every seed finished by then must have passed."""
+    exe = os.path.join(REF_DIR, "dropin_test_segreduce")
+    if not os.path.exists(exe):
+        pytest.skip("drop-in test binary not built")
+    try:
+        run = subprocess.run(["stdbuf", "-oL", exe], capture_output=True,
+                             text=True, timeout=25)
+        out = run.stdout
+    except subprocess.TimeoutExpired as e:
+        out = (e.stdout or b"").decode() if isinstance(e.stdout, bytes) \
+            else (e.stdout or "")
+    assert "Reduction error" not in out
+    assert out.count("passed") >= 2
