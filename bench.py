@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 # one ncu capture of a 2^26-item case of the same workload
 # (profiles/segreduce_k_fp32_c2.md), divided by that case's algorithmic
 # bytes; DRAM traffic grows in proportion to the units processed.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0026
+TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0037
 
 
 def measured_peak():
@@ -57,63 +57,75 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while running."""
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,"
-             "clocks_event_reasons.hw_slowdown,"
-             "clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,"
-             "clocks_event_reasons.sw_power_cap")
+    """Samples SM clocks and throttle reasons while the timed region runs:
+    NVML polled every few milliseconds from a thread (read-only queries), or
+    nvidia-smi when the NVML binding is missing."""
+    REASONS = {
+        "hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40,
+        "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4,
+    }
 
-    def __init__(self, index):
-        self.index = index
-        self.rows = []
-        self.proc = None
+    def __init__(self, uuid, index):
+        self.uuid, self.index = uuid, index
+        self.samples = []          # (time, sm_mhz, reasons_mask)
+        self.max_mhz = None
+        self.stop_flag = threading.Event()
         self.thread = None
+        self.window = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index),
-                 "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(
+                handle, pynvml.NVML_CLOCK_SM))
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) >= 7:
-                self.rows.append(parts)
+            def poll():
+                while not self.stop_flag.is_set():
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(
+                            handle, pynvml.NVML_CLOCK_SM)
+                        mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(
+                            handle)
+                        self.samples.append((time.perf_counter(), float(mhz),
+                                             int(mask)))
+                    except Exception:
+                        pass
+                    time.sleep(0.004)
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.thread = None
+
+    def mark(self, t_begin, t_end):
+        self.window = (t_begin, t_end)
 
     def stop(self):
-        if self.proc is None:
+        self.stop_flag.set()
+        if self.thread is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [],
-                    "note": "nvidia-smi unavailable"}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                 "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[0]))
-                smax.append(float(r[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, r[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        busy = sorted(sm)[len(sm) // 2:] if sm else []
-        return {"sm_mhz": statistics.median(busy) if busy else None,
-                "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                    "note": "NVML unavailable"}
+        self.thread.join(timeout=2)
+        inside = [s for s in self.samples
+                  if self.window and self.window[0] <= s[0] <= self.window[1]]
+        note = "sampled inside the timed region"
+        if len(inside) < 3:
+            inside = self.samples
+            note = ("timed region shorter than the sampling period: samples "
+                    "cover warm-up, timed steps and the profiling loop")
+        mask = 0
+        for s in inside:
+            mask |= s[2]
+        mhz = sorted(s[1] for s in inside)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None,
+                "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(k for k, bit in self.REASONS.items()
+                                  if mask & bit),
+                "samples": len(inside), "note": note}
 
 
 def cpu_sample(count=1 << 26, num_segments=1 << 21, seed=1):
@@ -173,14 +185,14 @@ def run_reference_cpu(args, rank, world):
 
 def workload_config(n_gpus):
     return {
-        "workload": "config 2: fp32 plus-segreduce, 268,435,456 items uniform "
-                    "in [-1,1), 8,388,608 segments, geometric lengths mean 32 "
-                    "with 5% empty, init 0 (per GPU)",
+        "workload": "config 2: fp32 plus-segreduce, %d items uniform in "
+                    "[-1,1), %d segments, geometric lengths mean 32 with 5%% "
+                    "empty, init 0 (per GPU)" % (COUNT, NUM_SEGMENTS),
         "items_per_gpu": COUNT, "segments_per_gpu": NUM_SEGMENTS,
         "sharding": "item range cut evenly over %d GPU(s); one 16-byte "
                     "boundary record per GPU exchanged per step" % n_gpus,
-        "l2": "inputs are 1.14 GB per GPU, larger than the 126 MB L2; no "
-              "flush between steps",
+        "l2": "inputs are %.2f GB per GPU, larger than the 126 MB L2; no "
+              "flush between steps" % ((COUNT * 4 + NUM_SEGMENTS * 8) / 1e9),
     }
 
 
@@ -280,6 +292,12 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
+    sampler = None
+    if rank == 0:
+        props = torch.cuda.get_device_properties(local_rank)
+        sampler = ClockSampler("GPU-" + str(props.uuid), local_rank)
+        sampler.start()
+
     values, seg, table = make_shard(rank, device)
     out = torch.empty(NUM_SEGMENTS, dtype=torch.float32, device=device)
     records = torch.empty(world * sharded.RECORD_BYTES, dtype=torch.uint8,
@@ -297,19 +315,19 @@ def run_ours(args, rank, world, local_rank):
     torch.cuda.synchronize()
     assert mgpu.workspace_status() == 0, "device-side status reported failure"
 
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
+    t_begin = time.perf_counter()
     start.record()
     for _ in range(args.steps):
         step()
     stop.record()
     torch.cuda.synchronize()
+    if sampler:
+        sampler.mark(t_begin, time.perf_counter())
     elapsed_ms = start.elapsed_time(stop)
     if world > 1:
         t = torch.tensor([elapsed_ms], device=device)
@@ -414,11 +432,17 @@ def run_ours(args, rank, world, local_rank):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--small", action="store_true",
+                        help="2^26 items / 2^21 segments per GPU: a case "
+                             "small enough for a full ncu capture")
     parser.add_argument("--impl", default="ours",
                         choices=["ours", "reference", "reference-cuda"])
     args = parser.parse_args()
+    if args.small:
+        global COUNT, NUM_SEGMENTS
+        COUNT, NUM_SEGMENTS = 1 << 26, 1 << 21
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
