@@ -77,6 +77,31 @@ int mgpu_b200_segreduce(int dtype, int op, const void* input_device, int count,
   void* stream);
 
 /*
+ * mgpu_b200_segreduce for callers that cannot allocate device memory (no
+ * counterpart in the reference, whose temporaries always come from
+ * context_t::alloc). Same arguments and results as mgpu_b200_segreduce minus
+ * the workspace: the scratch is a fixed block of
+ * mgpu_b200_static_scratch_bytes() bytes (4 MiB) of device memory that is
+ * part of the loaded library, so every GPU that loads the library holds it
+ * until the process exits. The call allocates and frees nothing.
+ *  - A problem whose scratch exceeds the block is refused with
+ *    MGPU_B200_E_WORKSPACE before anything is launched (4-byte types fit up
+ *    to the library's overall size limit; 8-byte types up to roughly 4e8
+ *    items + segments).
+ *  - All calls on one GPU share the block, which keeps the previous call's
+ *    contents; the kernels clear what must start at zero. Calls that overlap
+ *    on a GPU (two streams, two host threads) race on it: run them one after
+ *    the other, or use mgpu_b200_segreduce with a workspace per stream.
+ *  - The block's address is looked up on the first call made with a given
+ *    GPU current; make that first call outside any stream capture.
+ */
+size_t mgpu_b200_static_scratch_bytes(void);
+
+int mgpu_b200_segreduce_static(int dtype, int op, const void* input_device,
+  int count, const int* segments_device, int num_segments,
+  void* output_device, const void* init_host, void* stream);
+
+/*
  * Diagnostic form of mgpu_b200_segreduce: same arguments and result, but the
  * call waits for the device and reports how long its two kernels ran, as
  * measured by CUDA events on `stream`: the merge-path partitioner

@@ -18,6 +18,7 @@ from .binding import (  # noqa: F401
     segreduce,
     segreduce_host,
     segreduce_profile,
+    segreduce_static,
     spmv,
     transform_lbs,
     workspace_status,
@@ -26,5 +27,6 @@ from .binding import (  # noqa: F401
 __all__ = [
     "LibraryMissing", "MgpuError", "interval_expand", "lib_path",
     "load_balance_partitions", "load_balance_search", "load_library",
-    "segreduce", "segreduce_host", "segreduce_profile", "spmv", "transform_lbs", "workspace_status",
+    "segreduce", "segreduce_host", "segreduce_profile",
+    "segreduce_static", "spmv", "transform_lbs", "workspace_status",
 ]

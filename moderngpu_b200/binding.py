@@ -100,6 +100,12 @@ def _declare_optional(lib):
     lib.mgpu_b200_interval_expand.argtypes = [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_size_t,
         c_void_p]
+    lib.mgpu_b200_static_scratch_bytes.restype = c_size_t
+    lib.mgpu_b200_static_scratch_bytes.argtypes = []
+    lib.mgpu_b200_segreduce_static.restype = c_int
+    lib.mgpu_b200_segreduce_static.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_void_p]
     lib.mgpu_b200_shard_pack.restype = c_int
     lib.mgpu_b200_shard_pack.argtypes = [
         c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
@@ -175,6 +181,30 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
             dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
             num_segments, out.data_ptr(), ctypes.byref(init_c),
             workspace.data_ptr(), workspace.numel(), _stream(input.device)))
+    return out
+
+
+def segreduce_static(input, segments, op="plus", init=0, out=None):
+    """segreduce without a caller-supplied workspace and without any device
+    allocation inside the library: the scratch is a fixed 4 MiB block that
+    ships with the library (mgpu_b200_segreduce_static). For callers that must
+    not allocate at the point of the call. `out` should be preallocated by
+    such callers; it is created here only as a convenience. Calls that overlap
+    on one GPU race on the shared block."""
+    lib = load_library()
+    _require_cuda(input, "input")
+    _require_cuda(segments, "segments", torch.int32)
+    if input.dtype not in _DTYPES:
+        raise TypeError("unsupported dtype %s" % input.dtype)
+    if out is None:
+        out = torch.empty(segments.numel(), dtype=input.dtype,
+                          device=input.device)
+    init_c = _CTYPES[input.dtype](init)
+    with torch.cuda.device(input.device):
+        _check(lib.mgpu_b200_segreduce_static(
+            _DTYPES[input.dtype], _OPS[op], input.data_ptr(), input.numel(),
+            segments.data_ptr(), segments.numel(), out.data_ptr(),
+            ctypes.byref(init_c), _stream(input.device)))
     return out
 
 
