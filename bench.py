@@ -128,6 +128,15 @@ class ClockSampler:
                 "samples": len(inside), "note": note}
 
 
+def host_threads():
+    """Host cores this process may run on (a launcher may have pinned
+    OMP_NUM_THREADS to 1; the CPU arm asks for its threads explicitly)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_sample(count=1 << 26, num_segments=1 << 21, seed=1):
     """A bounded sample of the workload for the CPU arm, generated on the host
     with the same length and value distributions."""
@@ -155,7 +164,7 @@ def run_reference_cpu(args, rank, world):
         return
     import oracle
     values, seg = cpu_sample()
-    threads = oracle.max_threads()
+    threads = host_threads()
     oracle.segreduce(values, seg, threads=threads)        # warm
     for _ in range(max(args.warmup - 1, 0)):
         oracle.segreduce(values, seg, threads=threads)
@@ -403,7 +412,7 @@ def run_ours(args, rank, world, local_rank):
         if world == 1:
             import oracle
             cv, cs = cpu_sample()
-            threads = oracle.max_threads()
+            threads = host_threads()
             cpu_value, reps, spent = time_cpu(cv, cs, 10.0, threads)
             cpu = {"value": cpu_value, "unit": UNIT, "cores": threads,
                    "kind": "port",
