@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(nt)
 lbs_partition_k(segments_it segments, int count, int num_segments,
   uint32_t step, int num_partitions, int_t* partitions,
   uint32_t* clear_head, int clear_head_words,
-  uint32_t* clear_tiles, int words_per_tile) {
+  uint32_t* clear_tiles, int words_per_tile, int tile_stride) {
 
   const unsigned full = 0xffffffffu;
   const int lane = (int)(threadIdx.x & 31);
@@ -88,7 +88,7 @@ lbs_partition_k(segments_it segments, int count, int num_segments,
     partitions[k] = (int_t)((uint32_t)diag - starts);
     if(clear_tiles && k < last)
       for(int w = 0; w < words_per_tile; ++w)
-        clear_tiles[(size_t)k * words_per_tile + w] = 0;
+        clear_tiles[(size_t)k * tile_stride + w] = 0;
   };
 
   // Pending long run of this thread: diagonals [run_lo, run_hi], all with
@@ -182,7 +182,8 @@ template<typename segments_it, typename int_t>
 void launch_lbs_partition(segments_it segments, int count, int num_segments,
   int64_t spacing, int num_partitions, int_t* partitions, cudaStream_t stream,
   uint32_t* clear_head = nullptr, int clear_head_words = 0,
-  uint32_t* clear_tiles = nullptr, int words_per_tile = 0) {
+  uint32_t* clear_tiles = nullptr, int words_per_tile = 0,
+  int tile_stride = 0) {
   enum { nt = 128, per_thread = 16 };
   // One more index than there are segments: the virtual closing start.
   int num_ctas = (int)div_up((int64_t)num_segments + 1,
@@ -191,7 +192,8 @@ void launch_lbs_partition(segments_it segments, int count, int num_segments,
   if(num_partitions > 0)
     lbs_partition_k<nt, per_thread><<<num_ctas, nt, 0, stream>>>(segments,
       count, num_segments, step, num_partitions, partitions, clear_head,
-      clear_head_words, clear_tiles, words_per_tile);
+      clear_head_words, clear_tiles, words_per_tile,
+      tile_stride ? tile_stride : words_per_tile);
 }
 
 } // namespace detail

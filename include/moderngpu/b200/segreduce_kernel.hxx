@@ -13,7 +13,7 @@
 // output[j-1]: every item of segment j-1 lies in that tile or in earlier
 // ones. The last tile also writes the last segment.
 //
-// A CTA is nt consumer threads plus one producer warp.
+// A CTA is nt consumer threads plus one producer warp and two carry warps.
 //  * Producer (one lane): takes the next tile from a global ticket counter,
 //    reads its two partition values, and issues bulk asynchronous copies of
 //    the tile's item window and segment-start window from HBM into one of
@@ -29,10 +29,11 @@
 //      4. second sweep over the registers: values at segment ends are stored
 //         in place; a second pass over the segment starts copies them to
 //         output[] (coalesced);
-//      5. the value of the segment open at the tile's right edge is published
-//         in the tile-status array; the one output that needs items of
-//         earlier tiles is finished by a warp that looks back through that
-//         array (tile_state.hxx).
+//      5. two threads leave a small record for the CTA's carry warps, which
+//         publish the value of the segment open at the tile's right edge in
+//         the tile-status array and finish the one output that needs items
+//         of earlier tiles by looking back through that array
+//         (tile_state.hxx).
 //
 // Results: each segment is folded strictly left to right within a thread and
 // combined as op(earlier, later) everywhere else; `init` is written for empty
@@ -53,7 +54,8 @@ template<int nt_, int vt_, int stages_, int occ_>
 struct segreduce_tuning_t {
   enum { nt = nt_, vt = vt_, stages = stages_, occ = occ_,
     nv = nt_ * vt_ - 8 };
-  static_assert(nt_ % 32 == 0 && vt_ >= 4 && vt_ <= 31, "unsupported tile");
+  static_assert(nt_ % 32 == 0 && nt_ >= 128 && vt_ >= 4 && vt_ <= 31,
+    "unsupported tile");
 };
 
 namespace detail {
@@ -140,24 +142,26 @@ struct segreduce_args_t {
   uint64_t timeout_ns;    // bound on every device-side wait
 };
 
-// A finished tile hands the one output that may need earlier tiles, and the
-// publication of its inclusive value when it holds no segment start, to the
-// CTA's carry warp through a small ring of these records.
+// What a finished tile leaves for the CTA's carry warp: enough to finish the
+// one output that may depend on earlier tiles (the segment open at the tile's
+// left edge) and to publish the inclusive value of a tile without segment
+// starts. Two consumer threads of different warps fill it, so that no warp
+// carries a long serial tail; the decisions are taken by the carry warp.
 template<typename type_t>
-struct carry_req_t {
-  int tile;          // -1: no more requests
-  int flags;         // carry_* bits below
-  int out_index;     // output[] element to write when carry_out is set
+struct tile_edge_t {
+  int tile;
+  int a0, na;        // first item and number of items of the tile
+  int b0, nb;        // first segment start and number of starts of the tile
+  int has_first;     // the end marker of segment b0 - 1 lies in this tile
+  int prev0, p0;     // start offsets of segments b0 - 1 and b0
+  int closed;        // a segment start sits exactly on the tile's right edge
   int pad;
-  alignas(8) char lead[sizeof(type_t)];   // fold of the tile's leading run
-  alignas(8) char tail[sizeof(type_t)];   // fold of all the tile's items
+  alignas(8) char lead[sizeof(type_t)];   // fold of items [a0, p0) of the tile
+  alignas(8) char tail[sizeof(type_t)];   // fold of the run ending at a1 - 1
 };
-enum {
-  carry_out = 1,        // write output[out_index]
-  carry_has_lead = 2,   // the leading run has items in this tile
-  carry_need_left = 4,  // the segment began in an earlier tile
-  carry_partial = 8     // the tile published tile_partial
-};
+
+// Carry warps per CTA; tile k of a CTA goes to warp k % segreduce_carry_warps.
+enum { segreduce_carry_warps = 2 };
 
 template<typename tuning_t, typename type_t>
 struct segreduce_smem_t {
@@ -168,15 +172,15 @@ struct segreduce_smem_t {
     elem = (int)sizeof(type_t),
     wide = elem > 4 ? elem : 4,
     stage_bytes = (nv * wide + 8 * elem + 64 + 127) / 128 * 128,
-    ring = 4
+    ring = 32
   };
   struct fixed_t {
     uint64_t full[stages];
     uint64_t empty[stages];
-    uint64_t req_full[ring];
-    uint64_t req_empty[ring];
+    uint64_t edge_full[ring];   // consumers -> carry warp
+    uint64_t edge_free[ring];   // carry warp -> consumers
     tile_desc_t desc[stages];
-    carry_req_t<type_t> req[ring];
+    tile_edge_t<type_t> edge[ring];
     uint32_t flags[2][flag_words];
     int warp_head[warps];
     alignas(16) char warp_agg[warps * elem];
@@ -206,7 +210,8 @@ MGPU_DEVICE void load_chunk(const type_t* src, type_t (&v)[vt]) {
 
 template<typename tuning_t, typename type_t, typename source_t,
   typename segments_it, typename output_it, typename op_t>
-__global__ void __launch_bounds__(tuning_t::nt + 64, tuning_t::occ)
+__global__ void __launch_bounds__(tuning_t::nt + 32 + 32 * segreduce_carry_warps,
+  tuning_t::occ)
 segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   op_t> args) {
 
@@ -237,12 +242,12 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       fixed.desc[s].tile = -1;
     }
     for(int r = 0; r < ring; ++r) {
-      ptx::mbar_init(&fixed.req_full[r], 1);
-      ptx::mbar_init(&fixed.req_empty[r], 1);
+      ptx::mbar_init(&fixed.edge_full[r], 2);
+      ptx::mbar_init(&fixed.edge_free[r], 1);
     }
     ptx::fence_proxy_async();
   }
-  for(int i = tid; i < 2 * flag_words; i += nt + 64)
+  for(int i = tid; i < 2 * flag_words; i += nt + 32 + 32 * segreduce_carry_warps)
     (&fixed.flags[0][0])[i] = 0;
   __syncthreads();
 
@@ -382,35 +387,54 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
 
   //////////////////////////////////////////////////////////////////////////////
   // Carry warp: finishes, off the consumers' critical path, whatever needs
-  // values of earlier tiles.
+  // values of earlier tiles. One record per tile arrives through a small
+  // ring; a record whose tile is -1 ends the loop.
 
-  if(warp == warps + 1) {
-    for(int n = 0; ; ++n) {
+  if(warp > warps) {
+    for(int n = warp - warps - 1; ; n += segreduce_carry_warps) {
       int r = n % ring;
-      if(!ptx::mbar_wait(&fixed.req_full[r], (n / ring) & 1, args.timeout_ns))
+      if(!ptx::mbar_wait(&fixed.edge_full[r], (n / ring) & 1,
+        args.timeout_ns)) {
+        // Never act on a record that was not delivered.
         atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
-      carry_req_t<type_t> req = fixed.req[r];
+        break;
+      }
+      const tile_edge_t<type_t> e = fixed.edge[r];
       __syncwarp();
-      if(0 == lane) ptx::mbar_arrive(&fixed.req_empty[r]);
-      if(req.tile < 0) break;
+      if(0 == lane) ptx::mbar_arrive(&fixed.edge_free[r]);
+      if(e.tile < 0) break;
 
       type_t lead, tail;
-      memcpy(&lead, req.lead, sizeof(type_t));
-      memcpy(&tail, req.tail, sizeof(type_t));
+      memcpy(&lead, e.lead, sizeof(type_t));
+      memcpy(&tail, e.tail, sizeof(type_t));
+      // Segment b0 - 1 is written here unless it is empty (then the
+      // consumers wrote `init`); it needs earlier tiles when it began
+      // before a0. A tile without starts also owes its inclusive value.
+      const bool need_out = e.has_first && e.prev0 != e.p0;
+      const bool has_lead = e.p0 > e.a0 && e.na > 0;
+      const bool need_left = need_out && e.prev0 < e.a0 && e.tile > 0;
+      const bool partial = 0 == e.nb && e.tile > 0;
+      // First of all tell later tiles what this tile contributes to the
+      // segment open at its right edge. Publishing from here keeps the
+      // store's completion off the consumers' barriers.
+      if(0 == lane) {
+        if(e.closed) state.publish(e.tile, tile_closed);
+        else state.publish(e.tile, partial ? tile_partial : tile_inclusive,
+          tail);
+      }
       bool have = false;
       type_t carry = init;
-      if(req.tile > 0 && (req.flags & (carry_need_left | carry_partial)))
-        have = lookback(state, req.tile, op, carry, args.timeout_ns,
+      if(need_left || partial)
+        have = lookback(state, e.tile, op, carry, args.timeout_ns,
           args.header + 1);
       if(0 == lane) {
-        if(req.flags & carry_partial)
-          state.publish(req.tile, tile_inclusive,
+        if(partial)
+          state.publish(e.tile, tile_inclusive,
             have ? op(carry, tail) : tail);
-        if(req.flags & carry_out) {
+        if(need_out && e.b0 <= num_segments) {
           type_t result = lead;
-          if((req.flags & carry_need_left) && have)
-            result = (req.flags & carry_has_lead) ? op(carry, lead) : carry;
-          args.output[req.out_index] = result;
+          if(need_left && have) result = has_lead ? op(carry, lead) : carry;
+          args.output[e.b0 - 1] = result;
         }
       }
     }
@@ -423,19 +447,8 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   type_t* warp_agg = reinterpret_cast<type_t*>(fixed.warp_agg);
   const unsigned full_mask = 0xffffffffu;
   const uint32_t vt_mask = (1u << vt) - 1;
-  int requests = 0;     // used by thread 0 only
-
-  auto send_request = [&](const carry_req_t<type_t>& req) {
-    int r = requests % ring;
-    int use = requests / ring;
-    if(use > 0 &&
-      !ptx::mbar_wait(&fixed.req_empty[r], (use - 1) & 1, args.timeout_ns))
-      atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
-    fixed.req[r] = req;
-    ptx::mbar_arrive(&fixed.req_full[r]);
-    ++requests;
-  };
-
+  const int edge_thread_a = nt / 2, edge_thread_b = nt / 2 + 32;
+  int tiles_done = 0;
   for(int it = 0; ; ++it) {
     int s = it % stages;
     if(!ptx::mbar_wait(&fixed.full[s], (it / stages) & 1, args.timeout_ns))
@@ -478,17 +491,12 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       ptx::named_sync<1, nt>();
     }
 
-    // 1. Head flags, and `init` for empty segments.
+    // 1. Head flags.
     auto mark_heads = [&](auto start_of) {
-      for(int j = b0 + tid; j < jend; j += nt) {
-        int p = start_of(j);
-        if(j < b1) {
-          int rel = p - a0;
-          rel = rel < 0 ? 0 : (rel > na ? na : rel);
-          int w = lo + rel;
-          atomicOr(&flags[w >> 5], 1u << (w & 31));
-        }
-        if(j > 0 && start_of(j - 1) == p) args.output[j - 1] = init;
+      for(int j = b0 + tid; j < b1; j += nt) {
+        unsigned rel = (unsigned)(start_of(j) - a0);
+        int w = lo + (int)(rel < (unsigned)na ? rel : (unsigned)na);
+        atomicOr(&flags[w >> 5], 1u << (w & 31));
       }
     };
     if(all_staged) mark_heads(seg_start_staged);
@@ -498,7 +506,6 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       // the first item keeps padding to its left out of every fold.
       atomicOr(&flags[hi >> 5], 1u << (hi & 31));
       if(lo) atomicOr(&flags[lo >> 5], 1u << (lo & 31));
-      if(0 == na) state.publish(d.tile, tile_closed);
     }
     ptx::named_sync<1, nt>();
 
@@ -592,58 +599,62 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           vals[e1] = op(c, vals[e1]);
         }
       }
-      // The thread that owns the last item publishes the tile's state.
-      if(hi - 1 >= w0 && hi - 1 < w0 + vt) {
-        uint32_t code;
-        if(nb > 0) {
-          int p_last = all_staged ? seg_start_staged(b1 - 1) :
-            seg_start(b1 - 1);
-          code = p_last == a1 ? tile_closed : tile_inclusive;
-        } else code = d.tile ? tile_partial : tile_inclusive;
-        state.publish(d.tile, code, vals[hi - 1]);
-      }
     }
 
     for(int i = tid; i < flag_words; i += nt) flags_next[i] = 0;
     ptx::named_sync<1, nt>();
 
-    // 5. Outputs of the segments that end in this tile. The first one may
-    // need items of earlier tiles: that one goes to the carry warp.
-    carry_req_t<type_t> req;
-    if(0 == tid) {
-      req.tile = d.tile;
-      req.flags = 0;
-      req.out_index = b0 - 1;
-      req.pad = 0;
-      type_t lead = init, tail = init;
-      if(b0 >= 1 && b0 < jend) {
-        int prev0 = seg_start(b0 - 1);
-        int p0 = seg_start(b0);
-        if(prev0 != p0) {
-          req.flags |= carry_out;
-          int q0 = p0 - a0;
-          q0 = q0 < 0 ? 0 : (q0 > na ? na : q0);
-          if(q0 > 0) {
-            req.flags |= carry_has_lead;
-            lead = vals[lo + q0 - 1];
-          }
-          if(prev0 < a0) req.flags |= carry_need_left;
+    // 5. Outputs of the segments whose end marker (the next segment's start)
+    // lies in this tile: `init` for empty ones, the stored run end otherwise.
+    // The first one may need items of earlier tiles: the carry warp's job.
+    {
+      // Two threads of different warps fill the tile's edge record.
+      const int r = it % ring;
+      tile_edge_t<type_t>& e = fixed.edge[r];
+      if(edge_thread_a == tid || edge_thread_b == tid) {
+        if(it >= ring &&
+          !ptx::mbar_wait(&fixed.edge_free[r], (it / ring - 1) & 1,
+            args.timeout_ns))
+          atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+      }
+      if(edge_thread_a == tid) {
+        const bool has_first = b0 >= 1 && b0 < jend;
+        int prev0 = 0, p0 = 0;
+        type_t lead = init;
+        if(has_first) {
+          prev0 = all_staged ? seg_start_staged(b0 - 1) : seg_start(b0 - 1);
+          p0 = all_staged ? seg_start_staged(b0) : seg_start(b0);
+          unsigned q0 = (unsigned)(p0 - a0);
+          if(q0 > (unsigned)na) q0 = p0 < a0 ? 0u : (unsigned)na;
+          if(q0 > 0) lead = vals[lo + (int)q0 - 1];
         }
+        e.tile = d.tile; e.a0 = a0; e.na = na; e.b0 = b0; e.nb = nb;
+        e.has_first = has_first; e.prev0 = prev0; e.p0 = p0;
+        memcpy(e.lead, &lead, sizeof(type_t));
+        ptx::mbar_arrive(&fixed.edge_full[r]);
       }
-      if(0 == nb && d.tile > 0) {
-        req.flags |= carry_partial;
-        tail = vals[hi - 1];
+      if(edge_thread_b == tid) {
+        type_t tail = init;
+        if(na > 0) tail = vals[hi - 1];
+        int p_last = a1 - 1;
+        if(nb > 0)
+          p_last = all_staged ? seg_start_staged(b1 - 1) : seg_start(b1 - 1);
+        e.closed = p_last == a1;
+        memcpy(e.tail, &tail, sizeof(type_t));
+        ptx::mbar_arrive(&fixed.edge_full[r]);
       }
-      memcpy(req.lead, &lead, sizeof(type_t));
-      memcpy(req.tail, &tail, sizeof(type_t));
     }
     auto write_outputs = [&](auto start_of) {
-      for(int j = b0 + 1 + tid; j < jend; j += nt) {
+      for(int j = b0 + tid; j < jend; j += nt) {
+        if(0 == j) continue;
         int p = start_of(j);
-        if(start_of(j - 1) != p) {
-          int rel = p - a0;
-          rel = rel < 1 ? 1 : (rel > na ? na : rel);
-          args.output[j - 1] = vals[lo + rel - 1];
+        if(start_of(j - 1) == p) {
+          args.output[j - 1] = init;
+        } else if(j > b0) {
+          unsigned rel = (unsigned)(p - a0);
+          if(rel > (unsigned)na) rel = (unsigned)na;
+          if(rel < 1u) rel = 1u;
+          args.output[j - 1] = vals[lo + (int)rel - 1];
         }
       }
     };
@@ -651,13 +662,19 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     else write_outputs(seg_start);
     ptx::fence_proxy_async();
     ptx::mbar_arrive(&fixed.empty[s]);
-    if(0 == tid && req.flags) send_request(req);
+    ++tiles_done;
   }
-  if(0 == tid) {
-    carry_req_t<type_t> req;
-    memset(&req, 0, sizeof(req));
-    req.tile = -1;
-    send_request(req);
+  if(edge_thread_a == tid || edge_thread_b == tid) {
+    // One end-of-work record for each carry warp.
+    for(int n = tiles_done; n < tiles_done + segreduce_carry_warps; ++n) {
+      const int r = n % ring;
+      if(n >= ring &&
+        !ptx::mbar_wait(&fixed.edge_free[r], (n / ring - 1) & 1,
+          args.timeout_ns))
+        atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+      if(edge_thread_a == tid) fixed.edge[r].tile = -1;
+      ptx::mbar_arrive(&fixed.edge_full[r]);
+    }
   }
 }
 
@@ -728,12 +745,13 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
   launch_lbs_partition(segments, count, num_segments,
     (int64_t)tuning_t::nv, plan.num_tiles + 1, partitions, stream,
     header, 32, (uint32_t*)state,
-    (int)tile_state_traits<type_t>::clear_words);
+    (int)tile_state_traits<type_t>::clear_words,
+    (int)tile_state_traits<type_t>::stride_words);
   if(after_partition) cudaEventRecord(after_partition, stream);
 
   auto kernel = segreduce_k<tuning_t, type_t, source_t, segments_it,
     output_it, op_t>;
-  int threads = tuning_t::nt + 64;
+  int threads = tuning_t::nt + 32 + 32 * segreduce_carry_warps;
   int resident = resident_ctas<tuple<tuning_t, args_t> >(kernel, threads,
     (int)layout_t::total_bytes);
   int grid = plan.num_tiles < resident ? plan.num_tiles : resident;

@@ -46,8 +46,12 @@ struct tile_state_traits {
   enum { packed = sizeof(type_t) <= 4 &&
     std::is_trivially_copyable<type_t>::value };
   enum { slot_bytes = (sizeof(type_t) + 7) / 8 * 8 };
-  // 32-bit words per tile that must read zero before a launch.
-  enum { clear_words = packed ? 2 : 1 };
+  // 32-bit words per tile that must read zero before a launch, and the
+  // distance in 32-bit words between the slots of consecutive tiles. Each
+  // tile's status lives in its own 128-byte line: tiles that are in flight
+  // together belong to different SMs (and dies), which would otherwise write
+  // and poll one shared line.
+  enum { clear_words = packed ? 2 : 1, stride_words = packed ? 32 : 1 };
 };
 
 // Bytes of tile-status storage for num_tiles tiles.
@@ -55,7 +59,7 @@ template<typename type_t>
 inline size_t tile_state_bytes(int num_tiles) {
   typedef tile_state_traits<type_t> traits;
   size_t n = (size_t)num_tiles;
-  if(traits::packed) return n * 8;
+  if(traits::packed) return n * 4 * traits::stride_words;
   size_t codes = (n * 4 + 127) / 128 * 128;
   return codes + 2 * n * traits::slot_bytes;
 }
@@ -65,6 +69,7 @@ struct tile_state_t;
 
 template<typename type_t>
 struct tile_state_t<type_t, true> {
+  enum { stride = tile_state_traits<type_t>::stride_words / 2 };
   uint64_t* words;
 
   MGPU_DEVICE void bind(void* base, int) { words = (uint64_t*)base; }
@@ -72,13 +77,13 @@ struct tile_state_t<type_t, true> {
   MGPU_DEVICE void publish(int tile, uint32_t code, type_t value) const {
     uint32_t bits = 0;
     memcpy(&bits, &value, sizeof(type_t));
-    ptx::st_relaxed_u64(words + tile, ((uint64_t)code << 32) | bits);
+    ptx::st_relaxed_u64(words + (size_t)tile * stride, ((uint64_t)code << 32) | bits);
   }
   MGPU_DEVICE void publish(int tile, uint32_t code) const {
-    ptx::st_relaxed_u64(words + tile, (uint64_t)code << 32);
+    ptx::st_relaxed_u64(words + (size_t)tile * stride, (uint64_t)code << 32);
   }
   MGPU_DEVICE uint32_t peek(int tile, type_t& value) const {
-    uint64_t w = ptx::ld_relaxed_u64(words + tile);
+    uint64_t w = ptx::ld_relaxed_u64(words + (size_t)tile * stride);
     uint32_t bits = (uint32_t)w;
     memcpy(&value, &bits, sizeof(type_t));
     return (uint32_t)(w >> 32);
@@ -171,6 +176,33 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
   bool have = false;
   type_t acc = carry;
   int base = tile - 1;
+
+  // Common case: the tile just before has a segment start of its own, so its
+  // word is final as soon as it appears. Every lane reads the same word.
+  {
+    type_t value = carry;
+    uint32_t code = tile_empty;
+    uint64_t start = 0;
+    for(uint32_t spin = 0; ; ++spin) {
+      code = state.peek(base, value);
+      if(tile_empty != code) break;
+      if(spin > 16) __nanosleep(100);
+      if(31 == (spin & 31)) {
+        uint64_t now = __shfl_sync(full, ptx::global_timer_ns(), 0);
+        if(!start) start = now;
+        else if(now - start > timeout_ns) break;
+      }
+    }
+    code = __shfl_sync(full, code, 0);
+    value = shfl_any(value, 0);
+    if(tile_empty == code) {
+      if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);
+      return false;
+    }
+    if(tile_closed == code) return false;
+    if(tile_inclusive == code) { carry = value; return true; }
+  }
+
   while(true) {
     int idx = base - lane;
     uint32_t code = tile_closed;      // before tile 0: nothing to add
