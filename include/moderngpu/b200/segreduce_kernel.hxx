@@ -13,7 +13,7 @@
 // output[j-1]: every item of segment j-1 lies in that tile or in earlier
 // ones. The last tile also writes the last segment.
 //
-// A CTA is nt consumer threads plus one producer warp and two carry warps.
+// A CTA is nt consumer threads plus one producer warp and one carry warp.
 //  * Producer (one lane): takes the next tile from a global ticket counter,
 //    reads its two partition values, and issues bulk asynchronous copies of
 //    the tile's item window and segment-start window from HBM into one of
@@ -161,7 +161,7 @@ struct tile_edge_t {
 };
 
 // Carry warps per CTA; tile k of a CTA goes to warp k % segreduce_carry_warps.
-enum { segreduce_carry_warps = 2 };
+enum { segreduce_carry_warps = 1 };
 
 template<typename tuning_t, typename type_t>
 struct segreduce_smem_t {
@@ -272,6 +272,11 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       if(use > 0 &&
         !ptx::mbar_wait(&fixed.empty[s], (use - 1) & 1, args.timeout_ns))
         atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+      // The consumers wrote into this stage with ordinary stores; order those
+      // (observed through the barrier) before the bulk copy's writes. Doing
+      // it here rather than in every consumer keeps their pending global
+      // stores out of the stage's release.
+      ptx::fence_proxy_async();
 
       tile_desc_t d;
       d.tile = next_tile;
@@ -644,24 +649,36 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         ptx::mbar_arrive(&fixed.edge_full[r]);
       }
     }
-    auto write_outputs = [&](auto start_of) {
-      for(int j = b0 + tid; j < jend; j += nt) {
-        if(0 == j) continue;
-        int p = start_of(j);
-        if(start_of(j - 1) == p) {
-          args.output[j - 1] = init;
-        } else if(j > b0) {
-          unsigned rel = (unsigned)(p - a0);
-          if(rel > (unsigned)na) rel = (unsigned)na;
-          if(rel < 1u) rel = 1u;
-          args.output[j - 1] = vals[lo + (int)rel - 1];
-        }
-      }
+    // Each thread looks up at most one output per pass: the value is read
+    // from the stage first, so that in the usual case (no more segment
+    // starts than threads) the stage is released before the global stores.
+    auto lookup_output = [&](auto start_of, int j, type_t& value) -> bool {
+      if(0 == j) return false;
+      int p = start_of(j);
+      if(start_of(j - 1) == p) { value = init; return true; }
+      if(j == b0) return false;          // the carry warp writes this one
+      unsigned rel = (unsigned)(p - a0);
+      if(rel > (unsigned)na) rel = (unsigned)na;
+      if(rel < 1u) rel = 1u;
+      value = vals[lo + (int)rel - 1];
+      return true;
     };
-    if(all_staged) write_outputs(seg_start_staged);
-    else write_outputs(seg_start);
-    ptx::fence_proxy_async();
-    ptx::mbar_arrive(&fixed.empty[s]);
+    {
+      int j = b0 + tid;
+      for(; j + nt < jend; j += nt) {    // rare: more starts than threads
+        type_t value;
+        bool write = all_staged ? lookup_output(seg_start_staged, j, value) :
+          lookup_output(seg_start, j, value);
+        if(write) args.output[j - 1] = value;
+      }
+      type_t value;
+      bool write = false;
+      if(j < jend)
+        write = all_staged ? lookup_output(seg_start_staged, j, value) :
+          lookup_output(seg_start, j, value);
+      ptx::mbar_arrive(&fixed.empty[s]);
+      if(write) args.output[j - 1] = value;
+    }
     ++tiles_done;
   }
   if(edge_thread_a == tid || edge_thread_b == tid) {
