@@ -438,6 +438,105 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_other_config(args, rank, world, local_rank):
+    """Secondary lines for the other benchmark configurations (--config):
+    device-resident throughput and algorithmic HBM GB/s, CUDA events, max
+    over ranks. c1: int32 plus 1,048,576 items / 10,000 segments; c3: CSR spmv
+    fp32, 16,777,216 rows; c4: load-balancing search with ranks, 268,435,456
+    items / 4,194,304 segments; c5: fp64 max- and plus-segreduce on one
+    2^29-item shard per GPU of log-normal segments (2^32 items at 8 GPUs)."""
+    import torch
+    import torch.distributed as dist
+    import moderngpu_b200 as mgpu
+    from moderngpu_b200 import sharded, workloads
+
+    mgpu.load_library()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = args.config
+    steps = {}
+    if cfg == "c1":
+        v, s = workloads.config1(seed=0)
+        v, s = torch.from_numpy(v).to(device), torch.from_numpy(s).to(device)
+        out = torch.empty(s.numel(), dtype=v.dtype, device=device)
+        steps["int32 plus"] = (lambda: mgpu.segreduce(v, s, init=0, out=out),
+                               v.numel(),
+                               workloads.segreduce_bytes(v.numel(), s.numel(), 4))
+    elif cfg == "c3":
+        m, c, x, r = workloads.config3(seed=2, device=device)
+        y = torch.empty(r.numel(), dtype=m.dtype, device=device)
+        steps["spmv fp32 nnz=%d" % m.numel()] = (
+            lambda: mgpu.spmv(m, c, x, r, out=y), m.numel(),
+            workloads.spmv_bytes(m.numel(), r.numel(), x.numel(), 4))
+    elif cfg == "c4":
+        count = 1 << 28
+        s = workloads.config4(seed=3, device=device)
+        steps["lbs seg+rank"] = (lambda: mgpu.transform_lbs(count, s), count,
+                                 workloads.lbs_bytes(count, s.numel()))
+        steps["lbs seg only"] = (lambda: mgpu.load_balance_search(count, s),
+                                 count,
+                                 workloads.lbs_bytes(count, s.numel(), False))
+    elif cfg == "c5":
+        count = 1 << 29
+        v, starts = workloads.config5_shard(4, rank, count, device=device)
+        table = torch.cat([torch.zeros(1, dtype=torch.int32, device=device),
+                           starts]) if (rank > 0 or world > 1) else starts
+        if rank == 0 and world > 1:
+            table = torch.cat([torch.zeros(1, dtype=torch.int32,
+                                           device=device), starts])
+        records = torch.empty(world * sharded.RECORD_BYTES, dtype=torch.uint8,
+                              device=device)
+        nbytes = workloads.segreduce_bytes(count, table.numel(), 8)
+        for op, init in (("max", -1e300), ("plus", 0.0)):
+            if world == 1:
+                out = torch.empty(table.numel(), dtype=v.dtype, device=device)
+                steps["fp64 " + op] = (
+                    lambda op=op, init=init: mgpu.segreduce(
+                        v, table, op=op, init=init, out=out), count, nbytes)
+            else:
+                steps["fp64 " + op] = (
+                    lambda op=op, init=init: sharded.sharded_segreduce(
+                        v, table, op=op, init=init, records=records),
+                    count, nbytes)
+    peak, peak_kind = measured_peak()
+    results = []
+    for name, (fn, units, nbytes) in steps.items():
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a = torch.cuda.Event(enable_timing=True)
+        b = torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        results.append({"case": name, "ms_per_step": ms,
+                        "gitems_per_s": world * units / (ms * 1e-3) / 1e9,
+                        "algorithmic_bytes_per_gpu": nbytes,
+                        "hbm_gbs_per_gpu": gbs,
+                        "frac_of_%s_peak" % peak_kind: gbs / peak})
+    assert mgpu.workspace_status() == 0
+    if rank == 0:
+        print(json.dumps({"config": cfg, "n_gpus": world, "steps": args.steps,
+                          "note": "includes every launch of a step "
+                                  "(partitioner + kernel, plus record pack / "
+                                  "all-gather / fold when n_gpus > 1)",
+                          "results": results}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -446,6 +545,10 @@ def main():
     parser.add_argument("--small", action="store_true",
                         help="2^26 items / 2^21 segments per GPU: a case "
                              "small enough for a full ncu capture")
+    parser.add_argument("--config", default="c2",
+                        choices=["c1", "c2", "c3", "c4", "c5"],
+                        help="c2 (default) is the headline line; the others "
+                             "print a shorter secondary line")
     parser.add_argument("--impl", default="ours",
                         choices=["ours", "reference", "reference-cuda"])
     args = parser.parse_args()
@@ -459,6 +562,8 @@ def main():
         run_reference_cpu(args, rank, world)
     elif args.impl == "reference-cuda":
         run_reference_cuda(args, rank, world)
+    elif args.config != "c2":
+        run_other_config(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

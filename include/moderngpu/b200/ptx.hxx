@@ -112,6 +112,25 @@ __device__ __forceinline__ void st_relaxed_u64(uint64_t* p, uint64_t v) {
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v)
     : "memory");
 }
+// 16-byte accesses: one transaction each on this hardware when the address
+// is 16-byte aligned, which the tile-status protocol relies on for 8-byte
+// values (value and code travel together).
+__device__ __forceinline__ void ld_relaxed_v2u64(const void* p, uint64_t& a,
+  uint64_t& b) {
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];"
+    : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_v2u64(void* p, uint64_t a,
+  uint64_t b) {
+  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};"
+    :: "l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p)
+    : "memory");
+  return v;
+}
 __device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p)

@@ -78,6 +78,27 @@ void spmv(matrix_it matrix, columns_it columns, vector_it vector, int count,
   segments_it segments, int num_segments, output_it output,
   context_t& context) {
   typedef typename std::iterator_traits<matrix_it>::value_type type_t;
+  typedef typename std::iterator_traits<columns_it>::value_type col_t;
+  typedef typename std::iterator_traits<vector_it>::value_type vec_t;
+  constexpr bool arrays = std::is_pointer<matrix_it>::value &&
+    std::is_pointer<columns_it>::value && std::is_pointer<vector_it>::value &&
+    std::is_floating_point<type_t>::value &&
+    std::is_same<typename std::remove_cv<vec_t>::type, type_t>::value &&
+    std::is_same<typename std::remove_cv<col_t>::type, int>::value &&
+    std::is_same<launch_arg_t, empty_t>::value;
+  if constexpr (arrays) {
+    // Plain CSR arrays: matrix values and column indices are staged by bulk
+    // copies, x is gathered through the read-only path.
+    typedef typename detail::spmv_default_tuning<type_t>::type tuning_t;
+    detail::check_merged_size(count, num_segments);
+    detail::segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);
+    if(!plan.num_tiles) return;
+    mem_t<char> workspace(plan.bytes, context);
+    detail::spmv_source_t<type_t> source { matrix, columns, vector };
+    detail::segreduce_enqueue<tuning_t>(source, count, segments, num_segments,
+      output, plus_t<type_t>(), (type_t)0, workspace.data(), context.stream());
+    return;
+  }
   transform_segreduce<launch_arg_t>([=]MGPU_DEVICE(int index) {
     return matrix[index] * ldg(vector + columns[index]);
   }, count, segments, num_segments, output, plus_t<type_t>(), (type_t)0,

@@ -72,9 +72,15 @@ struct segreduce_default_tuning<type_t, 2> { typedef segreduce_tuning_t<256, 16,
 template<typename type_t>
 struct segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<256, 28, 2, 3> type; };
 template<typename type_t>
-struct segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 10, 3, 3> type; };
+struct segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 26, 2, 2> type; };
 template<typename type_t>
 struct segreduce_default_tuning<type_t, 16> { typedef segreduce_tuning_t<256, 5, 3, 3> type; };
+
+// spmv stages 4 more bytes per item, so its tiles are smaller.
+template<typename type_t, int size = (int)sizeof(type_t)>
+struct spmv_default_tuning { typedef segreduce_tuning_t<256, 20, 2, 2> type; };
+template<typename type_t>
+struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2> type; };
 
 ////////////////////////////////////////////////////////////////////////////////
 // Value sources.
@@ -85,6 +91,20 @@ struct array_source_t {
   enum { bulk = 1 };
   const type_t* data;
   MGPU_DEVICE type_t load(int index) const { return data[index]; }
+};
+
+// CSR spmv: the value of item i is matrix[i] * x[columns[i]]. matrix and
+// columns are staged by bulk copies like an array source; the consumers then
+// gather x and overwrite the staged matrix values with the products.
+template<typename type_t>
+struct spmv_source_t {
+  enum { bulk = 2 };
+  const type_t* data;       // matrix values
+  const int* columns;
+  const type_t* x;
+  MGPU_DEVICE type_t load(int index) const {
+    return data[index] * __ldg(x + columns[index]);
+  }
 };
 
 // Anything with operator[]: evaluated by the consumer threads.
@@ -124,6 +144,9 @@ struct tile_desc_t {
   int src_lo, src_hi;   // positions delivered by the bulk copy
   int ob, oe;           // segment indices whose offsets are staged
   int offs_byte;        // byte offset of the staged offsets in the stage
+  int cols_byte;        // spmv: byte offset of the staged column indices,
+  int cols_lo;          //   position of item a0 among them,
+  int cols_src_lo, cols_src_hi;   // positions delivered by the bulk copy
   int pad;
 };
 
@@ -163,7 +186,7 @@ struct tile_edge_t {
 // Carry warps per CTA; tile k of a CTA goes to warp k % segreduce_carry_warps.
 enum { segreduce_carry_warps = 1 };
 
-template<typename tuning_t, typename type_t>
+template<typename tuning_t, typename type_t, int source_kind = 1>
 struct segreduce_smem_t {
   enum {
     nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
@@ -171,7 +194,9 @@ struct segreduce_smem_t {
     flag_words = nt * vt / 32 + 2,
     elem = (int)sizeof(type_t),
     wide = elem > 4 ? elem : 4,
-    stage_bytes = (nv * wide + 8 * elem + 64 + 127) / 128 * 128,
+    // spmv stages one int32 column index per item on top of everything else.
+    cols_bytes = 2 == source_kind ? nv * 4 + 48 : 0,
+    stage_bytes = (nv * wide + 8 * elem + 64 + cols_bytes + 127) / 128 * 128,
     ring = 32
   };
   struct fixed_t {
@@ -215,7 +240,7 @@ __global__ void __launch_bounds__(tuning_t::nt + 32 + 32 * segreduce_carry_warps
 segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   op_t> args) {
 
-  typedef segreduce_smem_t<tuning_t, type_t> layout_t;
+  typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk> layout_t;
   typedef typename layout_t::fixed_t fixed_t;
   enum { nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
     nv = tuning_t::nv, warps = nt / 32, flag_words = layout_t::flag_words,
@@ -364,9 +389,39 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         d.oe = jhi;
       }
 
+      // spmv: the tile's column indices, whole granules of columns[].
+      uint32_t cols_bytes = 0;
+      const char* cols_src = nullptr;
+      char* cols_dst = nullptr;
+      d.cols_byte = d.cols_lo = d.cols_src_lo = d.cols_src_hi = 0;
+      if constexpr (2 == src_bulk) {
+        const int* cols = args.source.columns;
+        int mis = (int)(((uintptr_t)cols / 4) % 4);
+        int64_t u0 = (int64_t)d.a0 + mis;
+        int64_t ubase = u0 / 4 * 4;
+        d.cols_lo = (int)(u0 - ubase);
+        int64_t inner_lo = mis ? 4 : 0;
+        int64_t inner_hi = ((int64_t)count + mis) / 4 * 4;
+        int64_t c_lo = ubase > inner_lo ? ubase : inner_lo;
+        int64_t c_hi = ((int64_t)d.a1 + mis + 3) / 4 * 4;
+        if(c_hi > inner_hi) c_hi = inner_hi;
+        int offs_count = (jhi > jlo ? jhi - jlo : 0) + 8;
+        d.cols_byte = (d.offs_byte + offs_count * 4 + 15) / 16 * 16;
+        if(na > 0 && c_hi > c_lo) {
+          cols_bytes = (uint32_t)((c_hi - c_lo) * 4);
+          cols_src = (const char*)(cols + (c_lo - mis));
+          cols_dst = stage + d.cols_byte + (c_lo - ubase) * 4;
+          d.cols_src_lo = (int)(c_lo - ubase);
+          d.cols_src_hi = (int)(c_hi - ubase);
+        }
+      }
+
       fixed.desc[s] = d;
-      if(item_bytes + offs_bytes) {
-        ptx::mbar_arrive_expect_tx(&fixed.full[s], item_bytes + offs_bytes);
+      if(item_bytes + offs_bytes + cols_bytes) {
+        ptx::mbar_arrive_expect_tx(&fixed.full[s],
+          item_bytes + offs_bytes + cols_bytes);
+        if(cols_bytes)
+          ptx::bulk_load(cols_dst, cols_src, cols_bytes, &fixed.full[s]);
         if(item_bytes)
           ptx::bulk_load(item_dst, item_src, item_bytes, &fixed.full[s]);
         if(offs_bytes)
@@ -487,8 +542,26 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     const bool all_staged = !is_last && (b0 > 0 ? b0 - 1 : 0) >= ob &&
       b1 <= oe;
 
+    // Positions whose value is already in the stage buffer.
+    int src_lo = d.src_lo, src_hi = d.src_hi;
     if constexpr (!src_bulk) {
       for(int i = tid; i < na; i += nt) vals[i] = args.source.load(a0 + i);
+    }
+    if constexpr (2 == src_bulk) {
+      // Products in place: staged matrix value times the gathered x entry.
+      const int* cols_s = reinterpret_cast<const int*>(stage + d.cols_byte);
+      #pragma unroll 4
+      for(int i = tid; i < na; i += nt) {
+        int w = lo + i;
+        int wc = d.cols_lo + i;
+        type_t m = (w >= src_lo && w < src_hi) ? vals[w] :
+          args.source.data[a0 + i];
+        int c = (wc >= d.cols_src_lo && wc < d.cols_src_hi) ? cols_s[wc] :
+          args.source.columns[a0 + i];
+        vals[w] = m * __ldg(args.source.x + c);
+      }
+      src_lo = lo;
+      src_hi = hi;
     }
     if constexpr (!seg_bulk) {
       for(int j = ob + tid; j < oe; j += nt)
@@ -524,7 +597,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       const int w0 = tid * vt;
       int i_lo = lo > w0 ? lo - w0 : 0;
       int i_hi = hi - w0 < vt ? hi - w0 : vt;
-      const bool inside = w0 + i_lo >= d.src_lo && w0 + i_hi <= d.src_hi;
+      const bool inside = w0 + i_lo >= src_lo && w0 + i_hi <= src_hi;
       const bool fast = std::is_arithmetic<type_t>::value ?
         (i_lo < i_hi && inside) : (inside && 0 == i_lo && vt == i_hi);
       uint32_t bits = __funnelshift_r(flags[w0 >> 5], flags[(w0 >> 5) + 1],
@@ -546,11 +619,11 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         head = 0 != (bits & vt_mask);
         ends &= vt_mask;
       } else if(i_lo < i_hi) {
-        if constexpr (src_bulk) {
+        if constexpr (1 == src_bulk) {
           // Array elements outside the 16-byte-aligned interior.
           for(int i = i_lo; i < i_hi; ++i) {
             int w = w0 + i;
-            if(w < d.src_lo || w >= d.src_hi)
+            if(w < src_lo || w >= src_hi)
               vals[w] = args.source.load(a0 + (w - lo));
           }
         }
@@ -748,7 +821,7 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
   cudaStream_t stream, uint64_t timeout_ns = default_timeout_ns,
   cudaEvent_t after_partition = nullptr) {
 
-  typedef segreduce_smem_t<tuning_t, type_t> layout_t;
+  typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk> layout_t;
   typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t>
     args_t;
   segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);

@@ -41,34 +41,37 @@ enum : uint32_t {
 
 template<typename type_t>
 struct tile_state_traits {
-  // Value and code travel in one 64-bit word when the value fits in 32 bits;
-  // otherwise the code is released after the value has been written.
-  enum { packed = sizeof(type_t) <= 4 &&
+  // Value and code travel in one 64-bit word when the value fits in 32 bits,
+  // in one aligned 16-byte access when it fits in 64 bits; otherwise the code
+  // is made visible after the value has been written.
+  enum { packed = sizeof(type_t) <= 8 &&
     std::is_trivially_copyable<type_t>::value };
-  enum { slot_bytes = (sizeof(type_t) + 7) / 8 * 8 };
+  // Wide layout of one tile: [code:4, pad:12][partial value][inclusive value],
+  // each value slot rounded up to 16 bytes.
+  enum { slot_bytes = ((int)sizeof(type_t) + 15) / 16 * 16 };
+  // Each tile's status lives in 128-byte lines of its own: tiles that are in
+  // flight together belong to different SMs (and dies), which would otherwise
+  // write and poll one shared line.
+  enum { tile_bytes = packed ? 128 : (16 + 2 * slot_bytes + 127) / 128 * 128 };
   // 32-bit words per tile that must read zero before a launch, and the
-  // distance in 32-bit words between the slots of consecutive tiles. Each
-  // tile's status lives in its own 128-byte line: tiles that are in flight
-  // together belong to different SMs (and dies), which would otherwise write
-  // and poll one shared line.
-  enum { clear_words = packed ? 2 : 1, stride_words = packed ? 32 : 1 };
+  // distance in 32-bit words between consecutive tiles.
+  enum { clear_words = packed ? (sizeof(type_t) <= 4 ? 2 : 4) : 1,
+    stride_words = tile_bytes / 4 };
 };
 
 // Bytes of tile-status storage for num_tiles tiles.
 template<typename type_t>
 inline size_t tile_state_bytes(int num_tiles) {
-  typedef tile_state_traits<type_t> traits;
-  size_t n = (size_t)num_tiles;
-  if(traits::packed) return n * 4 * traits::stride_words;
-  size_t codes = (n * 4 + 127) / 128 * 128;
-  return codes + 2 * n * traits::slot_bytes;
+  return (size_t)num_tiles * tile_state_traits<type_t>::tile_bytes;
 }
 
-template<typename type_t, bool packed = tile_state_traits<type_t>::packed>
+// layout: 1 = one 64-bit word, 2 = one 16-byte word, 0 = code + value slots.
+template<typename type_t, int layout = !tile_state_traits<type_t>::packed ? 0 :
+  (sizeof(type_t) <= 4 ? 1 : 2)>
 struct tile_state_t;
 
 template<typename type_t>
-struct tile_state_t<type_t, true> {
+struct tile_state_t<type_t, 1> {
   enum { stride = tile_state_traits<type_t>::stride_words / 2 };
   uint64_t* words;
 
@@ -91,17 +94,42 @@ struct tile_state_t<type_t, true> {
 };
 
 template<typename type_t>
-struct tile_state_t<type_t, false> {
-  enum { slot_bytes = tile_state_traits<type_t>::slot_bytes };
-  uint32_t* codes;
-  char* partials;
-  char* inclusives;
+struct tile_state_t<type_t, 2> {
+  enum { tile_bytes = tile_state_traits<type_t>::tile_bytes };
+  char* base;
 
-  MGPU_DEVICE void bind(void* base, int num_tiles) {
-    size_t n = (size_t)num_tiles;
-    codes = (uint32_t*)base;
-    partials = (char*)base + (n * 4 + 127) / 128 * 128;
-    inclusives = partials + n * slot_bytes;
+  MGPU_DEVICE void bind(void* base_, int) { base = (char*)base_; }
+
+  MGPU_DEVICE void publish(int tile, uint32_t code, type_t value) const {
+    uint64_t bits = 0;
+    memcpy(&bits, &value, sizeof(type_t));
+    ptx::st_relaxed_v2u64(base + (size_t)tile * tile_bytes, bits, code);
+  }
+  MGPU_DEVICE void publish(int tile, uint32_t code) const {
+    ptx::st_relaxed_v2u64(base + (size_t)tile * tile_bytes, 0, code);
+  }
+  MGPU_DEVICE uint32_t peek(int tile, type_t& value) const {
+    uint64_t bits, code;
+    ptx::ld_relaxed_v2u64(base + (size_t)tile * tile_bytes, bits, code);
+    memcpy(&value, &bits, sizeof(type_t));
+    return (uint32_t)code;
+  }
+};
+
+template<typename type_t>
+struct tile_state_t<type_t, 0> {
+  enum { slot_bytes = tile_state_traits<type_t>::slot_bytes,
+    tile_bytes = tile_state_traits<type_t>::tile_bytes };
+  char* base;
+
+  MGPU_DEVICE void bind(void* base_, int) { base = (char*)base_; }
+
+  MGPU_DEVICE uint32_t* code_of(int tile) const {
+    return (uint32_t*)(base + (size_t)tile * tile_bytes);
+  }
+  MGPU_DEVICE char* slot_of(int tile, uint32_t code) const {
+    return base + (size_t)tile * tile_bytes + 16 +
+      (tile_partial == code ? 0 : slot_bytes);
   }
 
   static MGPU_DEVICE void put(char* slot, const type_t& value) {
@@ -120,20 +148,20 @@ struct tile_state_t<type_t, false> {
   }
 
   MGPU_DEVICE void publish(int tile, uint32_t code, type_t value) const {
-    char* slot = (tile_partial == code ? partials : inclusives) +
-      (size_t)tile * slot_bytes;
-    put(slot, value);
-    ptx::st_release_u32(codes + tile, code);
+    put(slot_of(tile, code), value);
+    ptx::st_release_u32(code_of(tile), code);
   }
   MGPU_DEVICE void publish(int tile, uint32_t code) const {
-    ptx::st_release_u32(codes + tile, code);
+    ptx::st_release_u32(code_of(tile), code);
   }
+  // Polls stay cheap (a relaxed load); the fence that orders the value loads
+  // after the code is paid only once the code says a value is there.
   MGPU_DEVICE uint32_t peek(int tile, type_t& value) const {
-    uint32_t code = ptx::ld_acquire_u32(codes + tile);
-    if(tile_partial == code)
-      take(partials + (size_t)tile * slot_bytes, value);
-    else if(tile_inclusive == code)
-      take(inclusives + (size_t)tile * slot_bytes, value);
+    uint32_t code = ptx::ld_relaxed_u32(code_of(tile));
+    if(tile_partial == code || tile_inclusive == code) {
+      __threadfence();
+      take(slot_of(tile, code), value);
+    }
     return code;
   }
 };

@@ -73,28 +73,24 @@ int segreduce_op(int op, const void* input, int count, const int* segments,
 }
 
 ////////////////////////////////////////////////////////////////////////////////
-// spmv: products matrix[i] * x[columns[i]] evaluated by the reduction kernel's
+// spmv: matrix values and column indices staged by bulk copies, products
+// matrix[i] * x[columns[i]] formed in shared memory by the reduction kernel's
 // consumer threads (reference: src/moderngpu/kernel_segreduce.hxx:285-298).
 
 template<typename type_t>
-struct spmv_product_t {
-  const type_t* matrix;
-  const int* columns;
-  const type_t* x;
-  typedef type_t value_type;
-  MGPU_DEVICE type_t operator[](int index) const {
-    return matrix[index] * __ldg(x + columns[index]);
-  }
-};
+size_t spmv_bytes(int nnz, int rows) {
+  detail::segreduce_plan_t<typename detail::spmv_default_tuning<type_t>::type,
+    type_t> plan(nnz, rows);
+  return plan.bytes;
+}
 
 template<typename type_t>
 int spmv_typed(const void* matrix, const int* columns, const void* x, int nnz,
   const int* row_starts, int rows, void* y, void* workspace,
   cudaStream_t stream) {
-  typedef typename type_tuning<type_t>::type tuning_t;
-  typedef spmv_product_t<type_t> product_t;
-  detail::iterator_source_t<product_t, type_t> source {
-    product_t { (const type_t*)matrix, columns, (const type_t*)x } };
+  typedef typename detail::spmv_default_tuning<type_t>::type tuning_t;
+  detail::spmv_source_t<type_t> source { (const type_t*)matrix, columns,
+    (const type_t*)x };
   try {
     detail::segreduce_enqueue<tuning_t>(source, nnz, row_starts, rows,
       (type_t*)y, plus_t<type_t>(), (type_t)0, workspace, stream,
@@ -420,7 +416,10 @@ int segreduce_dispatch(int dtype, int op, const void* input, int count,
 extern "C" {
 
 size_t mgpu_b200_spmv_workspace_bytes(int dtype, int nnz, int rows) {
-  return mgpu_b200_segreduce_workspace_bytes(dtype, nnz, rows);
+  if(!sizes_ok(nnz, rows)) return 0;
+  if(MGPU_B200_F32 == dtype) return spmv_bytes<float>(nnz, rows);
+  if(MGPU_B200_F64 == dtype) return spmv_bytes<double>(nnz, rows);
+  return 0;
 }
 
 int mgpu_b200_spmv(int dtype, const void* matrix_device,
