@@ -91,6 +91,50 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src,
        "r"(smem_addr(bar)) : "memory");
 }
 
+// L2 residency hints. Streaming inputs are read once: marking their copies
+// evict-first leaves the L2 to data that is reused (the x vector of spmv,
+// which is gathered with evict-last).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;"
+    : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;"
+    : "=l"(policy));
+  return policy;
+}
+
+__device__ __forceinline__ void bulk_load_hint(void* smem_dst,
+  const void* gmem_src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+    "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes"
+    ".L2::cache_hint [%0], [%1], %2, [%3], %4;"
+    :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes),
+       "r"(smem_addr(bar)), "l"(policy) : "memory");
+}
+
+// Read-only load of a 4- or 8-byte value with an L2 policy.
+template<typename type_t>
+__device__ __forceinline__ type_t ld_nc_hint(const type_t* p, uint64_t policy) {
+  static_assert(sizeof(type_t) == 4 || sizeof(type_t) == 8, "4 or 8 bytes");
+  type_t v;
+  if constexpr (sizeof(type_t) == 4) {
+    uint32_t bits;
+    asm volatile("ld.global.nc.L2::cache_hint.b32 %0, [%1], %2;"
+      : "=r"(bits) : "l"(p), "l"(policy));
+    memcpy(&v, &bits, 4);
+  } else {
+    uint64_t bits;
+    asm volatile("ld.global.nc.L2::cache_hint.b64 %0, [%1], %2;"
+      : "=l"(bits) : "l"(p), "l"(policy));
+    memcpy(&v, &bits, 8);
+  }
+  return v;
+}
+
 ////////////////////////////////////////////////////////////////////////////////
 // Named barrier over `count` threads (a multiple of 32) of the CTA.
 

@@ -282,6 +282,8 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   if(warp == warps) {
     if(lane) return;
     const int64_t total = (int64_t)count + num_segments;
+    // Items (and spmv's matrix and column arrays) are read exactly once.
+    const uint64_t stream_policy = ptx::l2_policy_evict_first();
     // The next ticket and its two partition values are fetched one
     // iteration ahead, so their latency hides behind the wait for a free
     // stage buffer.
@@ -421,9 +423,11 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         ptx::mbar_arrive_expect_tx(&fixed.full[s],
           item_bytes + offs_bytes + cols_bytes);
         if(cols_bytes)
-          ptx::bulk_load(cols_dst, cols_src, cols_bytes, &fixed.full[s]);
+          ptx::bulk_load_hint(cols_dst, cols_src, cols_bytes, &fixed.full[s],
+            stream_policy);
         if(item_bytes)
-          ptx::bulk_load(item_dst, item_src, item_bytes, &fixed.full[s]);
+          ptx::bulk_load_hint(item_dst, item_src, item_bytes, &fixed.full[s],
+            stream_policy);
         if(offs_bytes)
           ptx::bulk_load(stage + d.offs_byte, offs_src, offs_bytes,
             &fixed.full[s]);
@@ -550,15 +554,32 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     if constexpr (2 == src_bulk) {
       // Products in place: staged matrix value times the gathered x entry.
       const int* cols_s = reinterpret_cast<const int*>(stage + d.cols_byte);
-      #pragma unroll 4
-      for(int i = tid; i < na; i += nt) {
-        int w = lo + i;
-        int wc = d.cols_lo + i;
-        type_t m = (w >= src_lo && w < src_hi) ? vals[w] :
-          args.source.data[a0 + i];
-        int c = (wc >= d.cols_src_lo && wc < d.cols_src_hi) ? cols_s[wc] :
-          args.source.columns[a0 + i];
-        vals[w] = m * __ldg(args.source.x + c);
+      const uint64_t keep_policy = ptx::l2_policy_evict_last();
+      // Batches of `batch` items per thread: all column indices first, then
+      // all gathers (independent loads in flight together), then the stores.
+      enum { batch = vt < 10 ? vt : 10 };
+      for(int first = tid; first < na; first += nt * batch) {
+        int c[batch];
+        type_t m[batch], xv[batch];
+        #pragma unroll
+        for(int k = 0; k < batch; ++k) {
+          int i = first + k * nt;
+          if(i < na) {
+            int w = lo + i;
+            int wc = d.cols_lo + i;
+            m[k] = (w >= src_lo && w < src_hi) ? vals[w] :
+              args.source.data[a0 + i];
+            c[k] = (wc >= d.cols_src_lo && wc < d.cols_src_hi) ? cols_s[wc] :
+              args.source.columns[a0 + i];
+          }
+        }
+        #pragma unroll
+        for(int k = 0; k < batch; ++k)
+          if(first + k * nt < na)
+            xv[k] = ptx::ld_nc_hint(args.source.x + c[k], keep_policy);
+        #pragma unroll
+        for(int k = 0; k < batch; ++k)
+          if(first + k * nt < na) vals[lo + first + k * nt] = m[k] * xv[k];
       }
       src_lo = lo;
       src_hi = hi;
