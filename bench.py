@@ -393,7 +393,7 @@ def run_ours(args, rank, world, local_rank):
             recs = gathered.cpu().numpy().view("uint64").reshape(world, 2)
             flags = [int(f) for f in recs[:, 1]]
             for k in sharded.fold_plan(flags, rank):
-                part = recs[k, :1].view("float32")[0]
+                part = float(recs[k, :1].view("float32")[0])
                 ho[-1] = part if flags[rank] & sharded.LAST_EMPTY \
                     else ho[-1] + part
     e2e_s = (time.perf_counter() - t0) / e2e_steps
