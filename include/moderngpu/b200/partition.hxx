@@ -22,6 +22,7 @@
 // saves a memset launch.
 #pragma once
 #include "runtime.hxx"
+#include "ptx.hxx"
 
 BEGIN_MGPU_NAMESPACE
 
@@ -72,6 +73,8 @@ lbs_partition_k(segments_it segments, int count, int num_segments,
   uint32_t* clear_head, int clear_head_words,
   uint32_t* clear_tiles, int words_per_tile, int tile_stride) {
 
+  // Let a dependent kernel (the reduction) set itself up meanwhile.
+  ptx::grid_launch_dependents();
   const unsigned full = 0xffffffffu;
   const int lane = (int)(threadIdx.x & 31);
   const uint32_t total = (uint32_t)count + (uint32_t)num_segments;

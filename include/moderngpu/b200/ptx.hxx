@@ -91,6 +91,18 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src,
        "r"(smem_addr(bar)) : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic
+// stream-serialization attribute may start while its predecessor in the
+// stream is still running; it must call grid_dependency_wait() before it
+// touches anything the predecessor writes. The predecessor calls
+// grid_launch_dependents() once it no longer minds company on the SMs.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // L2 residency hints. Streaming inputs are read once: marking their copies
 // evict-first leaves the L2 to data that is reused (the x vector of spmv,
 // which is gathered with evict-last).

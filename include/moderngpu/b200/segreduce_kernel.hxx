@@ -275,6 +275,9 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   for(int i = tid; i < 2 * flag_words; i += nt + 32 + 32 * segreduce_carry_warps)
     (&fixed.flags[0][0])[i] = 0;
   __syncthreads();
+  // Everything above ran while the partitioner was still at work; what
+  // follows reads its output.
+  ptx::grid_dependency_wait();
 
   //////////////////////////////////////////////////////////////////////////////
   // Producer warp: tickets, partition lookups, bulk copies.
@@ -869,7 +872,19 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
 
   args_t args { source, segments, output, op, init, count, num_segments,
     plan.num_tiles, partitions, header, state, timeout_ns };
-  kernel<<<grid, threads, layout_t::total_bytes, stream>>>(args);
+  // Launched as a programmatic dependent of the partitioner: its CTAs start,
+  // initialise their barriers and wait inside the kernel.
+  cudaLaunchConfig_t config = { };
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(threads);
+  config.dynamicSmemBytes = layout_t::total_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  throw_on_error(cudaLaunchKernelEx(&config, kernel, args));
 }
 
 } // namespace detail
