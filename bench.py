@@ -538,6 +538,10 @@ def run_other_config(args, rank, world, local_rank):
 
 
 def main():
+    # NCCL announces its version on stdout at this debug level, which would
+    # put a second line next to the JSON line.
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
