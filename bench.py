@@ -47,6 +47,19 @@ FALLBACK_HBM_GBS = 6650.0
 TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0037
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """Write one JSON line to the process's original stdout."""
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text)
+
+
 def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
@@ -189,7 +202,7 @@ def run_reference_cpu(args, rank, world):
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(n_gpus):
@@ -212,8 +225,8 @@ def run_reference_cuda(args, rank, world):
     from moderngpu_b200 import workloads
     path = os.path.join(ROOT, "oracle", "_ref", "libmgpu_ref.so")
     if not os.path.exists(path):
-        print(json.dumps({"impl": "reference-cuda", "unavailable":
-                          "oracle/_ref/libmgpu_ref.so was not built"}))
+        emit({"impl": "reference-cuda", "unavailable":
+              "oracle/_ref/libmgpu_ref.so was not built"})
         return
     ref = ctypes.CDLL(path)
     torch.cuda.set_device(0)
@@ -270,7 +283,7 @@ def run_reference_cuda(args, rank, world):
                 "h2d_bytes_per_step": COUNT * 4 + NUM_SEGMENTS * 4,
                 "d2h_bytes_per_step": NUM_SEGMENTS * 4},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def make_shard(rank, device):
@@ -433,7 +446,7 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 
@@ -528,11 +541,11 @@ def run_other_config(args, rank, world, local_rank):
                         "frac_of_%s_peak" % peak_kind: gbs / peak})
     assert mgpu.workspace_status() == 0
     if rank == 0:
-        print(json.dumps({"config": cfg, "n_gpus": world, "steps": args.steps,
-                          "note": "includes every launch of a step "
-                                  "(partitioner + kernel, plus record pack / "
-                                  "all-gather / fold when n_gpus > 1)",
-                          "results": results}), flush=True)
+        emit({"config": cfg, "n_gpus": world, "steps": args.steps,
+              "note": "includes every launch of a step (partitioner + "
+                      "kernel, plus record pack / all-gather / fold when "
+                      "n_gpus > 1)",
+              "results": results})
     if world > 1:
         dist.destroy_process_group()
 
@@ -542,6 +555,12 @@ def main():
     # put a second line next to the JSON line.
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"
+    # Whatever else a library writes to stdout goes to stderr instead; the
+    # JSON line is written to the original stdout by emit().
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
