@@ -75,6 +75,9 @@ def load_library():
     lib.mgpu_b200_load_balance_partitions.restype = c_int
     lib.mgpu_b200_load_balance_partitions.argtypes = [
         c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lib.mgpu_b200_debug_lookback_timeout.restype = c_int
+    lib.mgpu_b200_debug_lookback_timeout.argtypes = [
+        c_void_p, c_int, ctypes.c_uint64, ctypes.POINTER(c_int), c_void_p]
     lib.mgpu_b200_debug_set_wait_limit_ns.restype = ctypes.c_uint64
     lib.mgpu_b200_debug_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
     _declare_optional(lib)

@@ -270,6 +270,20 @@ int segreduce_host_impl(int dtype, int op, const char* input, int count,
 }
 
 
+// Diagnostic kernel: one warp looks back from tile `tile` over a tile-status
+// array in which nothing was ever published, so its bounded wait must run out
+// and leave status_lookback_timeout in *status. Nothing spins forever and
+// nothing faults; the context stays usable.
+__global__ void lookback_probe_k(void* state_words, int tile,
+  uint64_t timeout_ns, uint32_t* status, int* returned) {
+  detail::tile_state_t<float> state;
+  state.bind(state_words, tile + 1);
+  float carry = 0;
+  bool have = detail::lookback(state, tile, plus_t<float>(), carry, timeout_ns,
+    status);
+  if(0 == threadIdx.x) *returned = have ? 1 : 0;
+}
+
 inline bool sizes_ok(int count, int num_segments) {
   return count >= 0 && num_segments >= 0 &&
     (int64_t)count + num_segments <= (int64_t)0x7fffffff - 65536;
@@ -362,6 +376,33 @@ int mgpu_b200_segreduce_profile(int dtype, int op, const void* input_device,
   }
   for(auto& e : ev) cudaEventDestroy(e);
   return code;
+}
+
+// Test hook (not part of the stable interface): runs the look-back of a
+// single warp against `tiles` unpublished tile-status words held in
+// workspace_device (at least 128 * tiles + 256 bytes, 128-byte aligned) with
+// the given bound on its wait, waits for it, and returns the status word the
+// kernel recorded (MGPU_B200_STATUS_LOOKBACK_TIMEOUT is the expected answer).
+int mgpu_b200_debug_lookback_timeout(void* workspace_device, int tiles,
+  uint64_t timeout_ns, int* status_host, void* stream) {
+  if(!workspace_device || !status_host || tiles < 1 || tiles > 1024 ||
+    (uintptr_t)workspace_device % 128)
+    return MGPU_B200_E_INVALID;
+  cudaStream_t s = (cudaStream_t)stream;
+  size_t bytes = (size_t)tiles * 128 + 256;
+  cudaError_t e = cudaMemsetAsync(workspace_device, 0, bytes, s);
+  if(cudaSuccess != e) return cuda_code(e);
+  char* base = (char*)workspace_device;
+  uint32_t* status = (uint32_t*)base;
+  int* returned = (int*)(base + 64);
+  lookback_probe_k<<<1, 32, 0, s>>>(base + 256, tiles, timeout_ns, status,
+    returned);
+  uint32_t word[17] = { };
+  e = cudaMemcpyAsync(word, base, sizeof(word), cudaMemcpyDeviceToHost, s);
+  if(cudaSuccess == e) e = cudaStreamSynchronize(s);
+  if(cudaSuccess != e) return cuda_code(e);
+  *status_host = (int)word[0];
+  return word[16] ? MGPU_B200_E_DEVICE_STATUS : MGPU_B200_OK;
 }
 
 int mgpu_b200_workspace_status(const void* workspace_device, void* stream,
