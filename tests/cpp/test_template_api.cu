@@ -1,0 +1,328 @@
+// Exercises the C++ template entry points with user functors, user types and
+// iterator adaptors -- the part of the drop-in surface that a C ABI cannot
+// reach -- and checks every result against a host loop written the way the
+// reference's own tests check theirs (tests/test_segreduce.cu:40-49).
+// Built by __graft_entry__.build() into tests/cpp/build/, run by
+// tests/test_template_api_gpu.py. Prints one line per case and
+// "FAILED <n>" / "ALL PASSED" at the end; exit code = number of failures.
+#include <moderngpu/kernel_segreduce.hxx>
+#include <moderngpu/kernel_load_balance.hxx>
+#include <moderngpu/kernel_intervalmove.hxx>
+
+using namespace mgpu;
+
+static int failures = 0;
+
+static void report(const char* name, bool ok) {
+  printf("%-44s %s\n", name, ok ? "ok" : "FAIL");
+  if(!ok) ++failures;
+}
+
+static std::vector<int> random_segments(int count, int num_segments, int seed) {
+  std::mt19937 rng(seed);
+  std::uniform_int_distribution<int> dist(0, count);
+  std::vector<int> s(num_segments);
+  s[0] = 0;
+  for(int i = 1; i < num_segments; ++i) s[i] = dist(rng);
+  std::sort(s.begin() + 1, s.end());
+  return s;
+}
+
+static int seg_end(const std::vector<int>& seg, int s, int count) {
+  return s + 1 < (int)seg.size() ? seg[s + 1] : count;
+}
+
+// A 24-byte value with a non-commutative-looking combine: keeps the best
+// three distances seen so far together with the index of the best one
+// (the shape of demo/cities.cu's best_t).
+struct best_t {
+  float d[3];
+  int idx[3];
+};
+struct combine_best_t {
+  MGPU_HOST_DEVICE best_t operator()(best_t a, best_t b) const {
+    best_t r;
+    int i = 0, j = 0;
+    for(int k = 0; k < 3; ++k) {
+      bool take_a = a.d[i] <= b.d[j];      // ties keep the earlier operand
+      r.d[k] = take_a ? a.d[i] : b.d[j];
+      r.idx[k] = take_a ? a.idx[i] : b.idx[j];
+      if(take_a) ++i; else ++j;
+    }
+    return r;
+  }
+};
+static bool same(const best_t& a, const best_t& b) {
+  for(int k = 0; k < 3; ++k)
+    if(a.d[k] != b.d[k] || a.idx[k] != b.idx[k]) return false;
+  return true;
+}
+
+int main() {
+  standard_context_t context(false);
+
+  const int count = 1000003, num_segments = 30011;
+  std::vector<int> seg = random_segments(count, num_segments, 42);
+  mem_t<int> d_seg = to_mem(seg, context);
+
+  // 1. lbs_segreduce, f(index, seg, rank) = seg + rank, init -1
+  //    (the call the reference's test keeps commented out, :11-13,29-30).
+  {
+    mem_t<int> out(num_segments, context);
+    lbs_segreduce([]MGPU_DEVICE(int index, int s, int rank) {
+      return s + rank;
+    }, count, d_seg.data(), num_segments, out.data(), plus_t<int>(), -1,
+      context);
+    std::vector<int> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < num_segments; ++s) {
+      int x = -1;
+      for(int i = seg[s]; i < seg_end(seg, s, count); ++i) {
+        int y = s + (i - seg[s]);
+        x = (i == seg[s]) ? y : x + y;
+      }
+      ok = ok && x == got[s];
+    }
+    report("lbs_segreduce seg+rank", ok);
+  }
+
+  // 2. lbs_segreduce with a cached per-segment tuple and an extra argument:
+  //    f = values[index] * weight[seg] + bias, max-reduced.
+  {
+    std::vector<int> values(count), weights(num_segments);
+    std::mt19937 rng(7);
+    for(int& v : values) v = (int)(rng() % 200) - 100;
+    for(int& w : weights) w = (int)(rng() % 7) - 3;
+    mem_t<int> d_values = to_mem(values, context);
+    mem_t<int> d_weights = to_mem(weights, context);
+    mem_t<int> out(num_segments, context);
+    const int* vp = d_values.data();
+    lbs_segreduce([=]MGPU_DEVICE(int index, int s, int rank, tuple<int> w,
+      int bias) {
+      return vp[index] * get<0>(w) + bias;
+    }, count, d_seg.data(), num_segments, make_tuple(d_weights.data()),
+      out.data(), maximum_t<int>(), -9999, context, 5);
+    std::vector<int> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < num_segments; ++s) {
+      int x = -9999;
+      for(int i = seg[s]; i < seg_end(seg, s, count); ++i) {
+        int y = values[i] * weights[s] + 5;
+        x = (i == seg[s]) ? y : std::max(x, y);
+      }
+      ok = ok && x == got[s];
+    }
+    report("lbs_segreduce cached tuple + arg, max", ok);
+  }
+
+  // 3. segreduce on a 24-byte user type with a user combine functor, a
+  //    launch_params_t in the launch slot (accepted, as demo/cities.cu:218
+  //    passes one) and a lambda load iterator.
+  {
+    mem_t<best_t> out(num_segments, context);
+    best_t init;
+    for(int k = 0; k < 3; ++k) { init.d[k] = 1e30f; init.idx[k] = -1; }
+    auto load = [=]MGPU_DEVICE(int index) {
+      best_t b;
+      b.d[0] = (float)((index * 2654435761u) >> 12);
+      b.idx[0] = index;
+      b.d[1] = b.d[2] = 1e30f;
+      b.idx[1] = b.idx[2] = -1;
+      return b;
+    };
+    transform_segreduce<launch_params_t<128, 3> >(load, count, d_seg.data(),
+      num_segments, out.data(), combine_best_t(), init, context);
+    std::vector<best_t> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < num_segments && ok; ++s) {
+      best_t x = init;
+      for(int i = seg[s]; i < seg_end(seg, s, count); ++i) {
+        best_t y;
+        y.d[0] = (float)(((unsigned)i * 2654435761u) >> 12);
+        y.idx[0] = i;
+        y.d[1] = y.d[2] = 1e30f;
+        y.idx[1] = y.idx[2] = -1;
+        x = (i == seg[s]) ? y : combine_best_t()(x, y);
+      }
+      ok = same(x, got[s]);
+    }
+    report("transform_segreduce 24-byte type, user op", ok);
+  }
+
+  // 4. Long segments with the 24-byte type: the carry between tiles goes
+  //    through the wide tile-status layout.
+  {
+    const int n = 2000000, ns = 5;
+    std::vector<int> lseg = random_segments(n, ns, 5);
+    mem_t<int> d_lseg = to_mem(lseg, context);
+    mem_t<best_t> out(ns, context);
+    best_t init;
+    for(int k = 0; k < 3; ++k) { init.d[k] = 1e30f; init.idx[k] = -1; }
+    auto load = [=]MGPU_DEVICE(int index) {
+      best_t b;
+      b.d[0] = (float)((index * 40503u) & 0xfffff);
+      b.idx[0] = index;
+      b.d[1] = b.d[2] = 1e30f;
+      b.idx[1] = b.idx[2] = -1;
+      return b;
+    };
+    transform_segreduce(load, n, d_lseg.data(), ns, out.data(),
+      combine_best_t(), init, context);
+    std::vector<best_t> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < ns; ++s) {
+      best_t x = init;
+      for(int i = lseg[s]; i < seg_end(lseg, s, n); ++i) {
+        best_t y;
+        y.d[0] = (float)(((unsigned)i * 40503u) & 0xfffff);
+        y.idx[0] = i;
+        y.d[1] = y.d[2] = 1e30f;
+        y.idx[1] = y.idx[2] = -1;
+        x = (i == lseg[s]) ? y : combine_best_t()(x, y);
+      }
+      ok = ok && same(x, got[s]);
+    }
+    report("24-byte type, segments spanning many tiles", ok);
+  }
+
+  // 5. segreduce with a store iterator as output and a strided iterator as
+  //    the segment table (segments need not be an array).
+  {
+    const int n = 500000, every = 125, ns = n / every;
+    std::vector<int> values(n);
+    for(int i = 0; i < n; ++i) values[i] = i % 17 - 8;
+    mem_t<int> d_values = to_mem(values, context);
+    mem_t<long long> out(ns, context);
+    long long* op = out.data();
+    segreduce(d_values.data(), n, strided_iterator_t<int>(0, every), ns,
+      make_store_iterator<int>([=]MGPU_DEVICE(int v, int index) {
+        op[index] = 10ll * v;
+      }), plus_t<int>(), 0, context);
+    std::vector<long long> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < ns; ++s) {
+      int x = 0;
+      for(int i = s * every; i < (s + 1) * every; ++i) x += values[i];
+      ok = ok && got[s] == 10ll * x;
+    }
+    report("store iterator output, strided segments", ok);
+  }
+
+  // 6. spmv template entry point with double.
+  {
+    const int rows = 20000, cols = 5000;
+    std::mt19937 rng(3);
+    std::vector<int> starts(rows), columns;
+    std::vector<double> matrix, x(cols);
+    for(double& v : x) v = (double)((int)(rng() % 9) - 4);
+    for(int r = 0; r < rows; ++r) {
+      starts[r] = (int)columns.size();
+      int len = rng() % 9 == 0 ? 0 : rng() % 40;
+      for(int k = 0; k < len; ++k) {
+        columns.push_back(rng() % cols);
+        matrix.push_back((double)((int)(rng() % 9) - 4));
+      }
+    }
+    mem_t<int> d_starts = to_mem(starts, context);
+    mem_t<int> d_columns = to_mem(columns, context);
+    mem_t<double> d_matrix = to_mem(matrix, context);
+    mem_t<double> d_x = to_mem(x, context);
+    mem_t<double> y(rows, context);
+    spmv(d_matrix.data(), d_columns.data(), d_x.data(), (int)matrix.size(),
+      d_starts.data(), rows, y.data(), context);
+    std::vector<double> got = from_mem(y);
+    bool ok = true;
+    for(int r = 0; r < rows; ++r) {
+      double acc = 0;
+      int end = r + 1 < rows ? starts[r + 1] : (int)matrix.size();
+      for(int i = starts[r]; i < end; ++i) acc += matrix[i] * x[columns[i]];
+      ok = ok && acc == got[r];     // small integers: exact in any order
+    }
+    report("spmv<double> (integer-valued, exact)", ok);
+  }
+
+  // 7. transform_lbs with cached iterators; interval_expand / gather /
+  //    scatter / move.
+  {
+    const int n = 300000, ns = 9000;
+    std::vector<int> iseg = random_segments(n, ns, 9);
+    mem_t<int> d_iseg = to_mem(iseg, context);
+    std::vector<int> seg_of(n), rank_of(n);
+    for(int s = 0; s < ns; ++s)
+      for(int i = iseg[s]; i < seg_end(iseg, s, n); ++i) {
+        seg_of[i] = s;
+        rank_of[i] = i - iseg[s];
+      }
+    std::vector<float> scale(ns);
+    for(int s = 0; s < ns; ++s) scale[s] = 0.5f * s;
+    mem_t<float> d_scale = to_mem(scale, context);
+    mem_t<float> d_out(n, context);
+    float* outp = d_out.data();
+    transform_lbs([=]MGPU_DEVICE(int index, int s, int rank,
+      tuple<float, int> cached) {
+      outp[index] = get<0>(cached) + (float)rank + (float)(index - get<1>(cached));
+    }, n, d_iseg.data(), ns, make_tuple(d_scale.data(), d_iseg.data()), context);
+    std::vector<float> got = from_mem(d_out);
+    bool ok = true;
+    for(int i = 0; i < n; ++i)
+      ok = ok && got[i] == scale[seg_of[i]] + 2.0f * rank_of[i];
+    report("transform_lbs with two cached iterators", ok);
+
+    mem_t<int> d_lbs(n, context);
+    load_balance_search(n, d_iseg.data(), ns, d_lbs.data(), context);
+    ok = from_mem(d_lbs) == seg_of;
+    report("load_balance_search", ok);
+
+    mem_t<float> d_expand(n, context);
+    interval_expand(d_scale.data(), n, d_iseg.data(), ns, d_expand.data(),
+      context);
+    got = from_mem(d_expand);
+    ok = true;
+    for(int i = 0; i < n; ++i) ok = ok && got[i] == scale[seg_of[i]];
+    report("interval_expand", ok);
+
+    // gather[s] / scatter[s]: where segment s's items live in a shuffled
+    // array (segments laid out in reverse order).
+    std::vector<int> where(ns);
+    int pos = 0;
+    for(int s = ns - 1; s >= 0; --s) {
+      where[s] = pos;
+      pos += seg_end(iseg, s, n) - iseg[s];
+    }
+    std::vector<int> source(n);
+    for(int i = 0; i < n; ++i) source[i] = i * 3 + 1;
+    mem_t<int> d_where = to_mem(where, context);
+    mem_t<int> d_source = to_mem(source, context);
+    mem_t<int> d_a(n, context), d_b(n, context), d_c(n, context);
+    interval_scatter(d_source.data(), n, d_iseg.data(), ns, d_where.data(),
+      d_a.data(), context);                     // a[where[s]+rank] = source[i]
+    interval_gather(d_a.data(), n, d_iseg.data(), ns, d_where.data(),
+      d_b.data(), context);                     // b[i] = a[where[s]+rank]
+    ok = from_mem(d_b) == source;
+    report("interval_scatter then interval_gather", ok);
+    interval_move(d_a.data(), n, d_iseg.data(), ns, d_iseg.data(),
+      d_where.data(), d_c.data(), context);     // c[seg[s]+r] = a[where[s]+r]
+    ok = from_mem(d_c) == source;
+    report("interval_move", ok);
+  }
+
+  // 8. load_balance_partitions through mem_t, and merge_path on the host.
+  {
+    int spacing = 777;
+    mem_t<int> mp = load_balance_partitions((int64_t)count, d_seg.data(),
+      num_segments, spacing, context);
+    std::vector<int> got = from_mem(mp);
+    bool ok = (int)got.size() == div_up(count + num_segments, spacing) + 1;
+    for(size_t k = 0; k < got.size() && ok; ++k) {
+      int diag = std::min(spacing * (int)k, count + num_segments);
+      ok = got[k] == merge_path<bounds_upper>(counting_iterator_t<int>(0),
+        count, seg.data(), num_segments, diag, less_t<int>());
+    }
+    report("load_balance_partitions vs host merge_path", ok);
+  }
+
+  context.synchronize();
+  if(failures) printf("FAILED %d\n", failures);
+  else printf("ALL PASSED\n");
+  return failures;
+}
