@@ -456,8 +456,8 @@ def run_other_config(args, rank, world, local_rank):
     device-resident throughput and algorithmic HBM GB/s, CUDA events, max
     over ranks. c1: int32 plus 1,048,576 items / 10,000 segments; c3: CSR spmv
     fp32, 16,777,216 rows; c4: load-balancing search with ranks, 268,435,456
-    items / 4,194,304 segments; c5: fp64 max- and plus-segreduce on one
-    2^29-item shard per GPU of log-normal segments (2^32 items at 8 GPUs)."""
+    items / 4,194,304 segments; c5: fp64 max- and plus-segreduce over 2^32 items of
+    log-normal segments held as 8 shards, 8/N per GPU (strong scaling)."""
     import torch
     import torch.distributed as dist
     import moderngpu_b200 as mgpu
@@ -492,27 +492,25 @@ def run_other_config(args, rank, world, local_rank):
                                  count,
                                  workloads.lbs_bytes(count, s.numel(), False))
     elif cfg == "c5":
-        count = 1 << 29
-        v, starts = workloads.config5_shard(4, rank, count, device=device)
-        table = torch.cat([torch.zeros(1, dtype=torch.int32, device=device),
-                           starts]) if (rank > 0 or world > 1) else starts
-        if rank == 0 and world > 1:
+        # The whole 2^32-item array, always as 8 shards of 2^29 items; each of
+        # the N ranks holds 8/N consecutive shards (strong scaling).
+        total_shards, count = 8, 1 << 29
+        per_rank = total_shards // world
+        shards, nbytes = [], 0
+        for j in range(per_rank):
+            g = rank * per_rank + j
+            v, starts = workloads.config5_shard(4, g, count, device=device)
             table = torch.cat([torch.zeros(1, dtype=torch.int32,
                                            device=device), starts])
-        records = torch.empty(world * sharded.RECORD_BYTES, dtype=torch.uint8,
-                              device=device)
-        nbytes = workloads.segreduce_bytes(count, table.numel(), 8)
+            shards.append((v, table))
+            nbytes += workloads.segreduce_bytes(count, table.numel(), 8)
+        outs = [torch.empty(t.numel(), dtype=torch.float64, device=device)
+                for _, t in shards]
         for op, init in (("max", -1e300), ("plus", 0.0)):
-            if world == 1:
-                out = torch.empty(table.numel(), dtype=v.dtype, device=device)
-                steps["fp64 " + op] = (
-                    lambda op=op, init=init: mgpu.segreduce(
-                        v, table, op=op, init=init, out=out), count, nbytes)
-            else:
-                steps["fp64 " + op] = (
-                    lambda op=op, init=init: sharded.sharded_segreduce(
-                        v, table, op=op, init=init, records=records),
-                    count, nbytes)
+            steps["fp64 %s, 2^32 items in 8 shards" % op] = (
+                lambda op=op, init=init: sharded.sharded_segreduce_multi(
+                    shards, op=op, init=init, outs=outs),
+                per_rank * count, nbytes)
     peak, peak_kind = measured_peak()
     results = []
     for name, (fn, units, nbytes) in steps.items():

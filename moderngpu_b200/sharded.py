@@ -140,6 +140,50 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records):
     return out
 
 
+def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
+                            workspace=None):
+    """Several consecutive shards per rank (CUDA tensors only).
+
+    shards: list of (values, table) pairs held by this rank, in array order;
+    every rank holds the same number k of shards, and rank r's shards are
+    shards r*k .. r*k+k-1 of the whole array. Used when one GPU's share of the
+    array exceeds what a single call can index (count + segments < 2^31), for
+    instance the whole 2^32-item array on one GPU as 8 shards. One all-gather
+    of k records per rank; the fold treats the world*k shards as one chain.
+    Returns the list of per-shard outputs."""
+    lib = binding.load_library()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    k = len(shards)
+    dev = shards[0][0].device
+    dtype = binding._DTYPES[shards[0][0].dtype]
+    stream = binding._stream(dev)
+    mine = torch.empty(k * RECORD_BYTES, dtype=torch.uint8, device=dev)
+    records = torch.empty(world * k * RECORD_BYTES, dtype=torch.uint8,
+                          device=dev)
+    results = []
+    with torch.cuda.device(dev):
+        for j, (values, table) in enumerate(shards):
+            out = binding.segreduce(values, table, op=op, init=init,
+                                    out=None if outs is None else outs[j],
+                                    workspace=workspace)
+            binding._check(lib.mgpu_b200_shard_pack(
+                dtype, out.data_ptr(), table.data_ptr(), table.numel(),
+                values.numel(), mine.data_ptr() + j * RECORD_BYTES, stream))
+            results.append(out)
+        if world > 1:
+            dist.all_gather_into_tensor(records, mine, group=group)
+        else:
+            records.copy_(mine)
+        init_c = binding._CTYPES[shards[0][0].dtype](init)
+        for j, (values, table) in enumerate(shards):
+            binding._check(lib.mgpu_b200_shard_fold(
+                dtype, binding._OPS[op], records.data_ptr(), rank * k + j,
+                world * k, results[j].data_ptr(), table.numel(),
+                ctypes.byref(init_c), stream))
+    return results
+
+
 def _sharded_host(values, table, op, init, group, rank, world, local_reduce):
     v = values.numpy()
     t = table.numpy()

@@ -93,3 +93,28 @@ def test_sharded_matches_oracle(oracle, kind, dtype, op):
     else:
         want = oracle.segreduce(values, seg32, op=op, init=-7).astype(np.float64)
         assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("kind,dtype,op", [
+    ("lognormal", "float64", "max"), ("few_long", "int64", "plus"),
+    ("one", "int32", "plus"),
+])
+def test_several_shards_on_one_gpu(mgpu, oracle, kind, dtype, op):
+    """The array cut into 5 shards that one GPU reduces one after the other
+    (how an array beyond the 2^31 index limit of a single call is handled);
+    the chain of boundary records is folded exactly as across GPUs."""
+    values, seg = make_problem(kind, np.dtype(dtype).type)
+    pieces = 5
+    shards, firsts = [], []
+    for r in range(pieces):
+        begin, end, first, table = sharded.shard_table(seg, values.size, r, pieces)
+        shards.append((torch.from_numpy(values[begin:end].copy()).cuda(),
+                       torch.from_numpy(table).cuda()))
+        firsts.append(first)
+    outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7)
+    got = np.zeros(seg.size, dtype=np.float64)
+    for first, out in zip(firsts, outs):
+        vals = out.cpu().numpy()[1:]
+        got[first:first + vals.size] = vals
+    want = oracle.segreduce(values, seg.astype(np.int32), op=op, init=-7)
+    assert np.array_equal(got, want.astype(np.float64))
