@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 # one ncu capture of a 2^26-item case of the same workload
 # (profiles/segreduce_k_fp32_c2.md), divided by that case's algorithmic
 # bytes; DRAM traffic grows in proportion to the units processed.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0037
+TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9988
 
 
 _RESULT_FD = None
