@@ -333,6 +333,83 @@ int main() {
     report("load_balance_partitions vs host merge_path", ok);
   }
 
+  // 9. Randomised sweep with deliberately tiny tiles (504 merged elements,
+  //    chosen through the launch slot), so that a few thousand items already
+  //    span many tiles: segment starts on tile edges, tiles made only of
+  //    segment starts, tiles without any, runs of empty segments, unaligned
+  //    array starts. int plus with init -1, bit-exact.
+  {
+    typedef segreduce_tuning_t<128, 4, 2, 4> tiny_t;
+    std::mt19937 rng(2024);
+    int bad_cases = 0, cases = 0;
+    for(int round = 0; round < 240; ++round) {
+      int n = (int)(rng() % 6000);
+      int ns = 1 + (int)(rng() % (round % 3 == 0 ? 4000 : 60));
+      int shift = (int)(rng() % 4);            // misalign both arrays
+      std::vector<int> rseg(ns);
+      rseg[0] = 0;
+      int mode = round % 4;
+      for(int i = 1; i < ns; ++i) {
+        if(0 == mode) rseg[i] = (int)(rng() % (n + 1));
+        else if(1 == mode) rseg[i] = std::min(n, (int)((long long)i * 504 / 3));
+        else if(2 == mode) rseg[i] = (rng() % 5) ? rseg[i - 1] : (int)(rng() % (n + 1));
+        else rseg[i] = n;                       // everything empty but one
+      }
+      std::sort(rseg.begin() + 1, rseg.end());
+      std::vector<int> vals(n + shift), segpad(ns + shift);
+      for(int& v : vals) v = (int)(rng() % 2001) - 1000;
+      for(int i = 0; i < ns; ++i) segpad[i + shift] = rseg[i];
+      mem_t<int> d_vals = to_mem(vals, context);
+      mem_t<int> d_rseg = to_mem(segpad, context);
+      mem_t<int> out(ns, context);
+      segreduce<tiny_t>((const int*)d_vals.data() + shift, n,
+        (const int*)d_rseg.data() + shift, ns, out.data(), plus_t<int>(), -1,
+        context);
+      std::vector<int> got = from_mem(out);
+      bool ok = true;
+      for(int s = 0; s < ns && ok; ++s) {
+        int x = -1;
+        for(int i = rseg[s]; i < seg_end(rseg, s, n); ++i)
+          x = (i == rseg[s]) ? vals[i + shift] : x + vals[i + shift];
+        ok = x == got[s];
+      }
+      ++cases;
+      if(!ok) {
+        ++bad_cases;
+        if(bad_cases < 4) printf("  tiny-tile case %d failed (n=%d ns=%d mode=%d shift=%d)\n", round, n, ns, mode, shift);
+      }
+    }
+    report("240 random cases with 504-element tiles", 0 == bad_cases);
+  }
+
+  // 10. The same with the 24-byte type and double, long and short segments.
+  {
+    typedef segreduce_tuning_t<128, 4, 2, 4> tiny_t;
+    std::mt19937 rng(99);
+    bool ok = true;
+    for(int round = 0; round < 40 && ok; ++round) {
+      int n = 1 + (int)(rng() % 20000);
+      int ns = 1 + (int)(rng() % (round % 2 ? 30 : 3000));
+      std::vector<int> rseg = random_segments(n, ns, 1000 + round);
+      std::vector<double> vals(n);
+      for(double& v : vals) v = (double)((int)(rng() % 4001) - 2000);
+      mem_t<double> d_vals = to_mem(vals, context);
+      mem_t<int> d_rseg = to_mem(rseg, context);
+      mem_t<double> out(ns, context);
+      segreduce<tiny_t>((const double*)d_vals.data(), n, d_rseg.data(), ns,
+        out.data(), round % 4 < 2 ? plus_t<double>() : plus_t<double>(), -1.0,
+        context);
+      std::vector<double> got = from_mem(out);
+      for(int s = 0; s < ns && ok; ++s) {
+        double x = -1.0;
+        for(int i = rseg[s]; i < seg_end(rseg, s, n); ++i)
+          x = (i == rseg[s]) ? vals[i] : x + vals[i];
+        ok = x == got[s];                 // integer-valued: exact
+      }
+    }
+    report("40 random double cases with tiny tiles", ok);
+  }
+
   context.synchronize();
   if(failures) printf("FAILED %d\n", failures);
   else printf("ALL PASSED\n");
