@@ -213,6 +213,32 @@ transform_lbs_k(func_t f, int count, segments_it segments, int num_segments,
   const int na = t.a1 - t.a0;
   const int ob = t.ob, oe = t.oe;
 
+  // Usual case: every segment start the tile refers to is staged and no item
+  // precedes the first segment, so the per-item work is two shared loads.
+  const bool simple = t.b0 > 0 && (t.b0 - 1) >= ob && t.b1 <= oe;
+  if(simple) {
+    const int* offs_by_seg = shared.offs - ob;
+    const int full_rounds = na / nt;        // rounds in which no thread idles
+    #pragma unroll
+    for(int i = 0; i < vt; ++i) {
+      if(i < full_rounds) {
+        int w = i * nt + tid;
+        int seg = shared.seg_of[w];
+        int index = t.a0 + w;
+        f(index, seg, index - offs_by_seg[seg],
+          mgpu::load(caching_iterators, seg), args...);
+      }
+    }
+    int w = full_rounds * nt + tid;
+    if(w < na) {
+      int seg = shared.seg_of[w];
+      int index = t.a0 + w;
+      f(index, seg, index - offs_by_seg[seg],
+        mgpu::load(caching_iterators, seg), args...);
+    }
+    return;
+  }
+
   #pragma unroll
   for(int i = 0; i < vt; ++i) {
     int w = i * nt + tid;

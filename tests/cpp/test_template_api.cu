@@ -339,7 +339,11 @@ int main() {
   //    segment starts, tiles without any, runs of empty segments, unaligned
   //    array starts. int plus with init -1, bit-exact.
   {
+#ifdef MGPU_TEST_ON_REFERENCE
+    typedef empty_t tiny_t;      // the reference picks its own tile shape
+#else
     typedef segreduce_tuning_t<128, 4, 2, 4> tiny_t;
+#endif
     std::mt19937 rng(2024);
     int bad_cases = 0, cases = 0;
     for(int round = 0; round < 240; ++round) {
@@ -384,7 +388,11 @@ int main() {
 
   // 10. The same with the 24-byte type and double, long and short segments.
   {
+#ifdef MGPU_TEST_ON_REFERENCE
+    typedef empty_t tiny_t;      // the reference picks its own tile shape
+#else
     typedef segreduce_tuning_t<128, 4, 2, 4> tiny_t;
+#endif
     std::mt19937 rng(99);
     bool ok = true;
     for(int round = 0; round < 40 && ok; ++round) {
