@@ -3,11 +3,10 @@
 // (src/moderngpu/kernel_segreduce.hxx:303-308 and the overload without
 // cached iterators :390-395). Empty segments yield `init`.
 //
-// The reference fuses the load-balancing search into its reduction tile
-// kernel. Here the functor is evaluated by transform_lbs into a temporary
-// array of count values (from context.alloc), which the single-pass
-// segmented reduction then folds; results are identical, at the cost of one
-// extra write and read of the values.
+// As in the reference, the load-balancing search is fused into the reduction
+// kernel: the consumers of a tile work out the segment and rank of every item
+// in shared memory, evaluate the functor in striped order (so that its loads
+// from index-addressed arrays coalesce) and fold the values in place.
 #pragma once
 #include "segreduce.hxx"
 #include "load_balance.hxx"
@@ -22,16 +21,18 @@ template<typename launch_arg_t = empty_t, typename func_t,
 void lbs_segreduce(func_t f, int count, segments_it segments,
   int num_segments, pointers_t caching_iterators, output_it output, op_t op,
   type_t init, context_t& context, args_t... args) {
-  typedef tuple_iterator_value_t<pointers_t> value_t;
-  mem_t<type_t> values(count, context);
-  type_t* values_data = values.data();
-  transform_lbs<launch_arg_t>(
-    [=]MGPU_DEVICE(int index, int seg, int rank, value_t cached,
-      args_t... rest) {
-      values_data[index] = f(index, seg, rank, cached, rest...);
-    }, count, segments, num_segments, caching_iterators, context, args...);
-  segreduce<launch_arg_t>((const type_t*)values_data, count, segments,
-    num_segments, output, op, init, context);
+  typedef typename detail::pick_segreduce_tuning<launch_arg_t, type_t,
+    typename detail::lbs_segreduce_default_tuning<type_t>::type>::type
+    tuning_t;
+  typedef detail::lbs_source_t<func_t, pointers_t, type_t, args_t...>
+    source_t;
+  detail::check_merged_size(count, num_segments);
+  detail::segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);
+  if(!plan.num_tiles) return;
+  mem_t<char> workspace(plan.bytes, context);
+  source_t source { f, caching_iterators, tuple<args_t...>(args...) };
+  detail::segreduce_enqueue<tuning_t>(source, count, segments, num_segments,
+    output, op, init, workspace.data(), context.stream());
 }
 
 template<typename launch_arg_t = empty_t, typename func_t,

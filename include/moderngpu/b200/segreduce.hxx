@@ -23,12 +23,15 @@ namespace detail {
 // A caller may pass segreduce_tuning_t<...> in the launch_arg_t slot to pick
 // the tile shape; launch boxes written for other architectures are accepted
 // and replaced by the Blackwell default.
-template<typename launch_arg_t, typename type_t>
+template<typename launch_arg_t, typename type_t,
+  typename default_t = typename segreduce_default_tuning<type_t>::type>
 struct pick_segreduce_tuning {
-  typedef typename segreduce_default_tuning<type_t>::type type;
+  typedef default_t type;
 };
-template<int nt, int vt, int stages, int occ, typename type_t>
-struct pick_segreduce_tuning<segreduce_tuning_t<nt, vt, stages, occ>, type_t> {
+template<int nt, int vt, int stages, int occ, typename type_t,
+  typename default_t>
+struct pick_segreduce_tuning<segreduce_tuning_t<nt, vt, stages, occ>, type_t,
+  default_t> {
   typedef segreduce_tuning_t<nt, vt, stages, occ> type;
 };
 

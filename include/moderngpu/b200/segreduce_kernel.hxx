@@ -82,6 +82,16 @@ struct spmv_default_tuning { typedef segreduce_tuning_t<256, 20, 2, 2> type; };
 template<typename type_t>
 struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2> type; };
 
+// lbs_segreduce keeps 4 more bytes per item in shared memory as well.
+template<typename type_t, int size = (int)sizeof(type_t)>
+struct lbs_segreduce_default_tuning {
+  typedef typename segreduce_default_tuning<type_t>::type type;
+};
+template<typename type_t>
+struct lbs_segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<256, 20, 2, 2> type; };
+template<typename type_t>
+struct lbs_segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2> type; };
+
 ////////////////////////////////////////////////////////////////////////////////
 // Value sources.
 
@@ -104,6 +114,30 @@ struct spmv_source_t {
   const type_t* x;
   MGPU_DEVICE type_t load(int index) const {
     return data[index] * __ldg(x + columns[index]);
+  }
+};
+
+// lbs_segreduce: the value of item i is f(i, seg, rank, cached..., args...)
+// where seg and rank come from a load-balancing search over the tile. The
+// consumers work the segment of every item out in shared memory (head ids +
+// running maximum, as the load-balancing kernels do) and evaluate f in
+// striped order; nothing is staged for the items themselves.
+template<typename func_t, typename pointers_t, typename type_t,
+  typename... args_t>
+struct lbs_source_t {
+  enum { bulk = 3 };
+  func_t f;
+  pointers_t caching;
+  tuple<args_t...> args;
+
+  template<size_t... idx>
+  MGPU_DEVICE type_t call(int index, int seg, int rank,
+    index_sequence<idx...>) const {
+    return (type_t)f(index, seg, rank, mgpu::load(caching, seg),
+      get<idx>(args)...);
+  }
+  MGPU_DEVICE type_t eval(int index, int seg, int rank) const {
+    return call(index, seg, rank, make_index_sequence<sizeof...(args_t)>());
   }
 };
 
@@ -195,7 +229,8 @@ struct segreduce_smem_t {
     elem = (int)sizeof(type_t),
     wide = elem > 4 ? elem : 4,
     // spmv stages one int32 column index per item on top of everything else.
-    cols_bytes = 2 == source_kind ? nv * 4 + 48 : 0,
+    // lbs_segreduce keeps one int32 segment id per item there instead.
+    cols_bytes = (2 == source_kind || 3 == source_kind) ? nv * 4 + 48 : 0,
     stage_bytes = (nv * wide + 8 * elem + 64 + cols_bytes + 127) / 128 * 128,
     ring = 32
   };
@@ -339,7 +374,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       const char* item_src = nullptr;
       char* item_dst = nullptr;
       int items_end;
-      if constexpr (src_bulk) {
+      if constexpr (1 == src_bulk || 2 == src_bulk) {
         enum { per16 = 16 / elem };
         const type_t* data = args.source.data;
         int mis = (int)(((uintptr_t)data / elem) % per16);
@@ -399,6 +434,10 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       const char* cols_src = nullptr;
       char* cols_dst = nullptr;
       d.cols_byte = d.cols_lo = d.cols_src_lo = d.cols_src_hi = 0;
+      if constexpr (3 == src_bulk) {
+        int offs_count = (jhi > jlo ? jhi - jlo : 0) + 8;
+        d.cols_byte = (d.offs_byte + offs_count * 4 + 15) / 16 * 16;
+      }
       if constexpr (2 == src_bulk) {
         const int* cols = args.source.columns;
         int mis = (int)(((uintptr_t)cols / 4) % 4);
@@ -551,7 +590,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
 
     // Positions whose value is already in the stage buffer.
     int src_lo = d.src_lo, src_hi = d.src_hi;
-    if constexpr (!src_bulk) {
+    if constexpr (0 == src_bulk) {
       for(int i = tid; i < na; i += nt) vals[i] = args.source.load(a0 + i);
     }
     if constexpr (2 == src_bulk) {
@@ -603,6 +642,17 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     };
     if(all_staged) mark_heads(seg_start_staged);
     else mark_heads(seg_start);
+    int* ids = reinterpret_cast<int*>(stage + d.cols_byte);
+    if constexpr (3 == src_bulk) {
+      // Among equal starts the last segment owns the items: its id is left
+      // at the head position.
+      for(int j = b0 + tid; j < b1; j += nt) {
+        int p = seg_start(j);
+        bool owner = j + 1 >= b1 || seg_start(j + 1) != p;
+        int w = p - a0;
+        if(owner && w >= 0 && w < na) ids[w] = j;
+      }
+    }
     if(0 == tid) {
       // Sentinels: the tile's right edge always ends a run, and a head at
       // the first item keeps padding to its left out of every fold.
@@ -610,6 +660,48 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       if(lo) atomicOr(&flags[lo >> 5], 1u << (lo & 31));
     }
     ptx::named_sync<1, nt>();
+
+    if constexpr (3 == src_bulk) {
+      // Segment of every item (running maximum of head ids: thread, warp,
+      // CTA), then the functor in striped order. lo is 0 for this source.
+      const int w0 = tid * vt;
+      uint32_t bits = __funnelshift_r(flags[w0 >> 5], flags[(w0 >> 5) + 1],
+        w0 & 31) & ((1u << vt) - 1);
+      if(w0 >= na) bits = 0;
+      else if(w0 + vt > na) bits &= (1u << (na - w0)) - 1;
+      int mine = bits ? ids[w0 + 31 - __clz(bits)] : -1;
+      int incl = mine;
+      #pragma unroll
+      for(int delta = 1; delta < 32; delta *= 2) {
+        int y = __shfl_up_sync(0xffffffffu, incl, delta);
+        if(lane >= delta) incl = max(incl, y);
+      }
+      int before = __shfl_up_sync(0xffffffffu, incl, 1);
+      if(0 == lane) before = -1;
+      if(31 == lane) fixed.warp_head[warp] = incl;
+      ptx::named_sync<1, nt>();
+      int cur = b0 - 1;
+      for(int k = 0; k < warp; ++k) cur = max(cur, fixed.warp_head[k]);
+      cur = max(cur, before);
+      if(w0 < na) {
+        #pragma unroll
+        for(int i = 0; i < vt; ++i) {
+          if((bits >> i) & 1) cur = ids[w0 + i];
+          if(w0 + i < na) ids[w0 + i] = cur;
+        }
+      }
+      ptx::named_sync<1, nt>();
+      for(int i = tid; i < na; i += nt) {
+        int seg = ids[i];
+        if(seg >= 0) {
+          int index = a0 + i;
+          vals[i] = args.source.eval(index, seg, index - seg_start(seg));
+        } else {
+          vals[i] = init;
+        }
+      }
+      ptx::named_sync<1, nt>();
+    }
 
     if(na > 0) {
       // 2. Per-thread fold of positions [w0, w0 + vt). The value of every

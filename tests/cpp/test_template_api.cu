@@ -418,6 +418,42 @@ int main() {
     report("40 random double cases with tiny tiles", ok);
   }
 
+  // 11. lbs_segreduce over many tiny tiles: the fused load-balancing search
+  //     must agree with the host on every (seg, rank) across tile edges.
+  {
+#ifdef MGPU_TEST_ON_REFERENCE
+    typedef empty_t tiny_t;
+#else
+    typedef segreduce_tuning_t<128, 4, 2, 4> tiny_t;
+#endif
+    std::mt19937 rng(515);
+    bool ok = true;
+    for(int round = 0; round < 120 && ok; ++round) {
+      int n = (int)(rng() % 9000);
+      int ns = 1 + (int)(rng() % (round % 3 == 0 ? 5000 : 80));
+      std::vector<int> rseg(ns);
+      rseg[0] = 0;
+      for(int i = 1; i < ns; ++i)
+        rseg[i] = (round % 2 && (rng() % 4)) ? rseg[i - 1] : (int)(rng() % (n + 1));
+      std::sort(rseg.begin() + 1, rseg.end());
+      mem_t<int> d_rseg = to_mem(rseg, context);
+      mem_t<long long> out(ns, context);
+      lbs_segreduce<tiny_t>([]MGPU_DEVICE(int index, int s, int rank) {
+        return (long long)s * 3 + rank * 5 + index % 7;
+      }, n, d_rseg.data(), ns, out.data(), plus_t<long long>(), -1ll, context);
+      std::vector<long long> got = from_mem(out);
+      for(int s = 0; s < ns && ok; ++s) {
+        long long x = -1;
+        for(int i = rseg[s]; i < seg_end(rseg, s, n); ++i) {
+          long long y = (long long)s * 3 + (i - rseg[s]) * 5 + i % 7;
+          x = (i == rseg[s]) ? y : x + y;
+        }
+        ok = x == got[s];
+      }
+    }
+    report("120 random lbs_segreduce cases, tiny tiles", ok);
+  }
+
   context.synchronize();
   if(failures) printf("FAILED %d\n", failures);
   else printf("ALL PASSED\n");
