@@ -41,9 +41,8 @@ METRIC = "segreduce_throughput_256M_fp32_items"
 UNIT = "Gitems/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the reduction kernel from
-# one ncu capture of a 2^26-item case of the same workload
-# (profiles/segreduce_k_fp32_c2.md), divided by that case's algorithmic
-# bytes; DRAM traffic grows in proportion to the units processed.
+# one ncu capture of a 2^26-item case of the same workload, divided by that
+# case's algorithmic bytes; DRAM traffic grows in proportion to the units processed.
 TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9988
 
 

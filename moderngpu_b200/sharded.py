@@ -56,7 +56,8 @@ def shard_table(segments, count, rank, world):
 
 
 def pack_record_host(out0_bits, table, count):
-    """Host mirror of mgpu_b200_shard_pack (used on CPU ranks in tests)."""
+    """The boundary record of a shard whose outputs are already on the host
+    (the host-buffer path): same flags as mgpu_b200_shard_pack."""
     flags = 0
     real = table.size > 1
     first = int(table[1]) if real else count
@@ -88,31 +89,21 @@ def fold_plan(flags, rank):
     return take
 
 
-_NP_OPS = {"plus": lambda a, b: a + b, "max": max, "min": min}
-
-
 def sharded_segreduce(values, table, op="plus", init=0, group=None,
-                      local_reduce=None, records=None):
+                      records=None):
     """Reduce this rank's shard and fold boundary partials across ranks.
 
-    values: this rank's items; table: its shard-local start table (see module
-    docstring). Returns the local outputs (table.numel() entries; entry 0 is
-    this rank's boundary partial, owned by an earlier rank).
-
-    On CUDA tensors every step runs in the library's kernels and the exchange
-    is one all_gather of 16 bytes per rank. `local_reduce`, given only by the
-    CPU tests of the host logic, replaces step 1 for CPU tensors; the record
-    packing and the fold then run in their host mirrors."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    if values.is_cuda:
-        return _sharded_cuda(values, table, op, init, group, rank, world,
-                             records)
-    if local_reduce is None:
+    values: this rank's items (CUDA tensor); table: its shard-local start
+    table (see module docstring). Returns the local outputs (table.numel()
+    entries; entry 0 is this rank's boundary partial, owned by an earlier
+    rank). Every step runs in the library's kernels and the exchange is one
+    all_gather of 16 bytes per rank. There is no CPU path."""
+    if not values.is_cuda:
         raise binding.LibraryMissing(
             "sharded_segreduce runs on CUDA tensors only (no CPU fallback)")
-    return _sharded_host(values, table, op, init, group, rank, world,
-                         local_reduce)
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    return _sharded_cuda(values, table, op, init, group, rank, world, records)
 
 
 def _sharded_cuda(values, table, op, init, group, rank, world, records):
@@ -182,28 +173,3 @@ def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
                 world * k, results[j].data_ptr(), table.numel(),
                 ctypes.byref(init_c), stream))
     return results
-
-
-def _sharded_host(values, table, op, init, group, rank, world, local_reduce):
-    v = values.numpy()
-    t = table.numpy()
-    out = np.array(local_reduce(v, t, op, init))
-    bits = np.zeros(1, dtype=np.uint64)
-    bits.view(np.uint8)[:out.itemsize] = out[:1].view(np.uint8)
-    rec = pack_record_host(bits[0], t, v.size)
-    mine = torch.from_numpy(rec.view(np.int64).copy())
-    gathered = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
-    dist.all_gather(gathered, mine, group=group)
-    recs = np.stack([g.numpy().view(np.uint64) for g in gathered])
-    flags = [int(f) for f in recs[:, 1]]
-    fold = _NP_OPS[op]
-    acc = None
-    for k in fold_plan(flags, rank):
-        val = recs[k, :1].view(np.uint8)[:out.itemsize].view(out.dtype)[0]
-        acc = val if acc is None else fold(acc, val)
-    if acc is not None:
-        if flags[rank] & LAST_EMPTY:
-            out[-1] = acc
-        else:
-            out[-1] = fold(out[-1], acc)
-    return torch.from_numpy(out)

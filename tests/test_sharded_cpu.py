@@ -1,7 +1,7 @@
 """Host logic of the multi-GPU layer on CPU ranks (gloo, world_size 2 and 3):
 shard tables, boundary records, ownership and fold order. The per-shard
-reduction is done by the CPU oracle here (test stand-in only); on GPUs it is
-the library's kernel (tests/test_sharded_gpu.py)."""
+reduction is done by the CPU oracle inside this test (the library itself has
+no CPU path); on GPUs it is the library's kernel (tests/test_sharded_gpu.py)."""
 import os
 import socket
 
@@ -53,15 +53,28 @@ def worker(rank, world, port, kind, dtype_name, op, result_queue):
         begin, end, first, table = sharded.shard_table(seg, values.size, rank,
                                                        world)
 
-        def local_reduce(v, t, op_name, init):
-            return oracle.segreduce(v, t, op=op_name, init=init)
-
-        out = sharded.sharded_segreduce(
-            torch.from_numpy(values[begin:end].copy()),
-            torch.from_numpy(table), op=op, init=-7,
-            local_reduce=local_reduce)
+        # The per-shard reduction is the oracle's here (a stand-in that lives
+        # in this test only); everything after it is the host logic under
+        # test: record flags, exchange, who folds what and in which order.
+        local = values[begin:end]
+        out = oracle.segreduce(local, table, op=op, init=-7)
+        bits = np.zeros(1, dtype=np.uint64)
+        bits.view(np.uint8)[:out.itemsize] = out[:1].view(np.uint8)
+        rec = sharded.pack_record_host(bits[0], table, local.size)
+        gathered = [torch.zeros(2, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(rec.view(np.int64).copy()))
+        recs = np.stack([g.numpy().view(np.uint64) for g in gathered])
+        flags = [int(f) for f in recs[:, 1]]
+        fold = {"plus": lambda a, b: a + b, "max": max, "min": min}[op]
+        acc = None
+        for k in sharded.fold_plan(flags, rank):
+            val = recs[k, :1].view(np.uint8)[:out.itemsize].view(out.dtype)[0]
+            acc = val if acc is None else fold(acc, val)
+        if acc is not None:
+            out[-1] = acc if flags[rank] & sharded.LAST_EMPTY \
+                else fold(out[-1], acc)
         pieces = [None] * world
-        dist.all_gather_object(pieces, (first, out.numpy()[1:].tolist()))
+        dist.all_gather_object(pieces, (first, out[1:].tolist()))
         if rank == 0:
             got = np.full(seg.size, -12345, dtype=np.float64)
             for f, vals in pieces:
