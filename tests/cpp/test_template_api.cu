@@ -8,6 +8,7 @@
 #include <moderngpu/kernel_segreduce.hxx>
 #include <moderngpu/kernel_load_balance.hxx>
 #include <moderngpu/kernel_intervalmove.hxx>
+#include <moderngpu/kernel_scan.hxx>
 
 using namespace mgpu;
 
@@ -57,6 +58,15 @@ static bool same(const best_t& a, const best_t& b) {
     if(a.d[k] != b.d[k] || a.idx[k] != b.idx[k]) return false;
   return true;
 }
+
+// 2x2 integer matrices under multiplication: associative, not commutative.
+struct mat_t { long long a, b, c, d; };
+struct matmul_t {
+  MGPU_HOST_DEVICE mat_t operator()(mat_t x, mat_t y) const {
+    return mat_t { x.a * y.a + x.b * y.c, x.a * y.b + x.b * y.d,
+      x.c * y.a + x.d * y.c, x.c * y.b + x.d * y.d };
+  }
+};
 
 int main() {
   standard_context_t context(false);
@@ -452,6 +462,66 @@ int main() {
       }
     }
     report("120 random lbs_segreduce cases, tiny tiles", ok);
+  }
+
+  // 12. scan (the step before the path: lengths -> start offsets):
+  //     exclusive and inclusive, with and without the reduction, several
+  //     sizes around tile edges, a transform_scan and a non-commutative op.
+  {
+    bool ok = true;
+    std::mt19937 rng(77);
+    int sizes[] = { 0, 1, 31, 4095, 4096, 4097, 8192, 100000, 3000001 };
+    for(int n : sizes) {
+      std::vector<int> in(n);
+      for(int& v : in) v = (int)(rng() % 100);
+      mem_t<int> d_in = to_mem(in, context);
+      mem_t<int> d_exc(n, context), d_inc(n, context), d_total(1, context);
+      scan(d_in.data(), n, d_exc.data(), plus_t<int>(), d_total.data(), context);
+      scan<scan_type_inc>(d_in.data(), n, d_inc.data(), context);
+      std::vector<int> exc = from_mem(d_exc), inc = from_mem(d_inc);
+      int total = from_mem(d_total)[0], run = 0;
+      for(int i = 0; i < n && ok; ++i) {
+        ok = exc[i] == run;
+        run += in[i];
+        ok = ok && inc[i] == run;
+      }
+      ok = ok && total == run;
+    }
+    report("scan exclusive / inclusive / reduction", ok);
+
+    // lengths -> offsets -> segreduce, the way callers chain them.
+    const int ns = 50000;
+    std::vector<int> lengths(ns);
+    for(int& l : lengths) l = (rng() % 4) ? (int)(rng() % 60) : 0;
+    mem_t<int> d_len = to_mem(lengths, context);
+    mem_t<int> d_off(ns, context), d_count(1, context);
+    scan(d_len.data(), ns, d_off.data(), plus_t<int>(), d_count.data(), context);
+    int n = from_mem(d_count)[0];
+    mem_t<int> d_sums(ns, context);
+    transform_segreduce([]MGPU_DEVICE(int index) { return 1; }, n,
+      d_off.data(), ns, d_sums.data(), plus_t<int>(), 0, context);
+    report("scan -> segreduce recovers the lengths", from_mem(d_sums) == lengths);
+
+    // Order matters: 2x2 integer matrices under multiplication.
+    const int m = 40000;
+    mem_t<mat_t> d_mats(m, context), d_last(1, context);
+    auto make = []MGPU_DEVICE(int i) {
+      // Triangular with small entries: products stay exact in 64 bits.
+      return mat_t { 1, (long long)(i % 5) - 2, 0, 1 };
+    };
+    transform_scan<mat_t, scan_type_inc>(make, m, d_mats.data(), matmul_t(),
+      d_last.data(), context);
+    std::vector<mat_t> mats = from_mem(d_mats);
+    mat_t acc { 1, 0, 0, 1 };
+    bool mok = true;
+    for(int i = 0; i < m && mok; ++i) {
+      acc = matmul_t()(acc, mat_t { 1, (long long)(i % 5) - 2, 0, 1 });
+      mok = acc.a == mats[i].a && acc.b == mats[i].b && acc.c == mats[i].c &&
+        acc.d == mats[i].d;
+    }
+    mat_t last = from_mem(d_last)[0];
+    mok = mok && last.b == acc.b;
+    report("transform_scan, 32-byte non-commutative op", mok);
   }
 
   context.synchronize();
