@@ -490,6 +490,11 @@ def run_other_config(args, rank, world, local_rank):
         steps["lbs seg only"] = (lambda: mgpu.load_balance_search(count, s),
                                  count,
                                  workloads.lbs_bytes(count, s.numel(), False))
+    elif cfg == "scan":
+        x = torch.randint(0, 64, (1 << 28,), device=device, dtype=torch.int32)
+        out = torch.empty_like(x)
+        steps["exclusive scan int32, 2^28 items"] = (
+            lambda: mgpu.scan(x, out=out), x.numel(), 8 * x.numel())
     elif cfg == "c5":
         # The whole 2^32-item array, always as 8 shards of 2^29 items; each of
         # the N ranks holds 8/N consecutive shards (strong scaling).
@@ -566,7 +571,7 @@ def main():
                         help="2^26 items / 2^21 segments per GPU: a case "
                              "small enough for a full ncu capture")
     parser.add_argument("--config", default="c2",
-                        choices=["c1", "c2", "c3", "c4", "c5"],
+                        choices=["c1", "c2", "c3", "c4", "c5", "scan"],
                         help="c2 (default) is the headline line; the others "
                              "print a shorter secondary line")
     parser.add_argument("--impl", default="ours",

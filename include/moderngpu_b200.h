@@ -190,6 +190,21 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
   const void* init_host, void* reserved);
 
 /*
+ * mgpu::scan with plus (reference: src/moderngpu/kernel_scan.hxx:159-175):
+ * exclusive (inclusive == 0: output[i] = sum of input[0 .. i), output[0] = 0)
+ * or inclusive prefix sums of `count` elements of `dtype`; the usual way to
+ * turn segment lengths into the start offsets the calls above take.
+ * total_device, when not NULL, receives the sum of all elements (0 for
+ * count == 0). input and output may be the same array. Workspace:
+ * mgpu_b200_scan_workspace_bytes(dtype, count), 128-byte aligned.
+ */
+size_t mgpu_b200_scan_workspace_bytes(int dtype, int count);
+
+int mgpu_b200_scan(int dtype, int inclusive, const void* input_device,
+  int count, void* output_device, void* total_device, void* workspace_device,
+  size_t workspace_bytes, void* stream);
+
+/*
  * Multi-GPU layer (no counterpart in the reference, which is single-device).
  * The item range of a large problem is cut across GPUs; GPU r holds count_r
  * items and a shard-local start table `starts` whose entry 0 is always 0 and

@@ -15,6 +15,7 @@ from .binding import (  # noqa: F401
     load_balance_partitions,
     load_balance_search,
     load_library,
+    scan,
     segreduce,
     segreduce_host,
     segreduce_profile,
@@ -26,7 +27,7 @@ from .binding import (  # noqa: F401
 
 __all__ = [
     "LibraryMissing", "MgpuError", "interval_expand", "lib_path",
-    "load_balance_partitions", "load_balance_search", "load_library",
+    "load_balance_partitions", "load_balance_search", "load_library", "scan",
     "segreduce", "segreduce_host", "segreduce_profile",
     "segreduce_static", "spmv", "transform_lbs", "workspace_status",
 ]

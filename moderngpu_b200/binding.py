@@ -103,6 +103,12 @@ def _declare_optional(lib):
     lib.mgpu_b200_interval_expand.argtypes = [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_size_t,
         c_void_p]
+    lib.mgpu_b200_scan_workspace_bytes.restype = c_size_t
+    lib.mgpu_b200_scan_workspace_bytes.argtypes = [c_int, c_int]
+    lib.mgpu_b200_scan.restype = c_int
+    lib.mgpu_b200_scan.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_size_t,
+        c_void_p]
     lib.mgpu_b200_static_scratch_bytes.restype = c_size_t
     lib.mgpu_b200_static_scratch_bytes.argtypes = []
     lib.mgpu_b200_segreduce_static.restype = c_int
@@ -183,6 +189,30 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
         _check(lib.mgpu_b200_segreduce(
             dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
             num_segments, out.data_ptr(), ctypes.byref(init_c),
+            workspace.data_ptr(), workspace.numel(), _stream(input.device)))
+    return out
+
+
+def scan(input, inclusive=False, out=None, total=None, workspace=None):
+    """mgpu::scan with plus: prefix sums of a 1-D CUDA tensor.
+
+    Returns `out` (exclusive by default). `total`, a 1-element tensor of the
+    same dtype, receives the sum of all elements when given."""
+    lib = load_library()
+    _require_cuda(input, "input")
+    if input.dtype not in _DTYPES:
+        raise TypeError("unsupported dtype %s" % input.dtype)
+    count = input.numel()
+    if out is None:
+        out = torch.empty_like(input)
+    dtype = _DTYPES[input.dtype]
+    need = lib.mgpu_b200_scan_workspace_bytes(dtype, count)
+    if workspace is None:
+        workspace = _workspace(input.device, need)
+    with torch.cuda.device(input.device):
+        _check(lib.mgpu_b200_scan(
+            dtype, 1 if inclusive else 0, input.data_ptr(), count,
+            out.data_ptr(), None if total is None else total.data_ptr(),
             workspace.data_ptr(), workspace.numel(), _stream(input.device)))
     return out
 

@@ -4,6 +4,7 @@
 #include <moderngpu/kernel_segreduce.hxx>
 #include <moderngpu/kernel_load_balance.hxx>
 #include <moderngpu/kernel_intervalmove.hxx>
+#include <moderngpu/kernel_scan.hxx>
 #include <mutex>
 #include <vector>
 #include <algorithm>
@@ -284,6 +285,43 @@ __global__ void lookback_probe_k(void* state_words, int tile,
   if(0 == threadIdx.x) *returned = have ? 1 : 0;
 }
 
+template<typename type_t>
+int scan_typed(int inclusive, const void* input, int count, void* output,
+  void* total, void* workspace, cudaStream_t stream) {
+  typedef typename detail::scan_default_tuning<type_t>::type tuning_t;
+  try {
+    if(total) {
+      if(inclusive)
+        detail::scan_enqueue<tuning_t, scan_type_inc, type_t>(
+          (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
+          (type_t*)total, workspace, stream, g_timeout_ns);
+      else
+        detail::scan_enqueue<tuning_t, scan_type_exc, type_t>(
+          (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
+          (type_t*)total, workspace, stream, g_timeout_ns);
+    } else {
+      discard_iterator_t<type_t> nowhere;
+      if(inclusive)
+        detail::scan_enqueue<tuning_t, scan_type_inc, type_t>(
+          (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
+          nowhere, workspace, stream, g_timeout_ns);
+      else
+        detail::scan_enqueue<tuning_t, scan_type_exc, type_t>(
+          (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
+          nowhere, workspace, stream, g_timeout_ns);
+    }
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
+  }
+  return last_launch_code();
+}
+
+template<typename type_t>
+size_t scan_bytes(int count) {
+  return detail::scan_workspace_bytes<
+    typename detail::scan_default_tuning<type_t>::type, type_t>(count);
+}
+
 inline bool sizes_ok(int count, int num_segments) {
   return count >= 0 && num_segments >= 0 &&
     (int64_t)count + num_segments <= (int64_t)0x7fffffff - 65536;
@@ -547,6 +585,41 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
     return MGPU_B200_E_INVALID;
   return segreduce_host_impl(dtype, op, (const char*)input_host, count,
     segments_host, num_segments, (char*)output_host, init_host);
+}
+
+size_t mgpu_b200_scan_workspace_bytes(int dtype, int count) {
+  if(count < 0) return 0;
+  switch(dtype) {
+    case MGPU_B200_F32: return scan_bytes<float>(count);
+    case MGPU_B200_F64: return scan_bytes<double>(count);
+    case MGPU_B200_I32: return scan_bytes<int32_t>(count);
+    case MGPU_B200_I64: return scan_bytes<int64_t>(count);
+  }
+  return 0;
+}
+
+int mgpu_b200_scan(int dtype, int inclusive, const void* input_device,
+  int count, void* output_device, void* total_device, void* workspace_device,
+  size_t workspace_bytes, void* stream) {
+  if(count < 0 || (count && (!input_device || !output_device)) ||
+    !workspace_device || (uintptr_t)workspace_device % 128)
+    return MGPU_B200_E_INVALID;
+  size_t need = mgpu_b200_scan_workspace_bytes(dtype, count);
+  if(!need) return MGPU_B200_E_UNSUPPORTED;
+  if(workspace_bytes < need) return MGPU_B200_E_WORKSPACE;
+  if(0 == count && !total_device) return MGPU_B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch(dtype) {
+    case MGPU_B200_F32: return scan_typed<float>(inclusive, input_device,
+      count, output_device, total_device, workspace_device, s);
+    case MGPU_B200_F64: return scan_typed<double>(inclusive, input_device,
+      count, output_device, total_device, workspace_device, s);
+    case MGPU_B200_I32: return scan_typed<int32_t>(inclusive, input_device,
+      count, output_device, total_device, workspace_device, s);
+    case MGPU_B200_I64: return scan_typed<int64_t>(inclusive, input_device,
+      count, output_device, total_device, workspace_device, s);
+  }
+  return MGPU_B200_E_UNSUPPORTED;
 }
 
 } // extern "C"
