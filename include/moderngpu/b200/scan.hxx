@@ -38,7 +38,7 @@ namespace detail {
 template<typename type_t, int size = (int)sizeof(type_t)>
 struct scan_default_tuning { typedef scan_tuning_t<128, 4, 4> type; };
 template<typename type_t>
-struct scan_default_tuning<type_t, 4> { typedef scan_tuning_t<256, 16, 4> type; };
+struct scan_default_tuning<type_t, 4> { typedef scan_tuning_t<512, 20, 2> type; };
 template<typename type_t>
 struct scan_default_tuning<type_t, 8> { typedef scan_tuning_t<256, 8, 4> type; };
 
