@@ -68,6 +68,35 @@ struct matmul_t {
   }
 };
 
+// A 16-byte value: complex-like pair of doubles, added component-wise.
+struct pair_t { double re, im; };
+struct pair_plus_t {
+  MGPU_HOST_DEVICE pair_t operator()(pair_t a, pair_t b) const {
+    return pair_t { a.re + b.re, a.im + b.im };
+  }
+};
+
+template<typename type_t, typename op_t>
+static bool check_small_type(int n, int ns, int seed, op_t op, type_t init,
+  context_t& context) {
+  std::vector<int> rseg = random_segments(n, ns, seed);
+  std::mt19937 rng(seed);
+  std::vector<type_t> vals(n);
+  for(type_t& v : vals) v = (type_t)((int)(rng() % 7) - 3);
+  mem_t<type_t> d_vals = to_mem(vals, context);
+  mem_t<int> d_rseg = to_mem(rseg, context);
+  mem_t<type_t> out(ns, context);
+  segreduce(d_vals.data(), n, d_rseg.data(), ns, out.data(), op, init, context);
+  std::vector<type_t> got = from_mem(out);
+  for(int s = 0; s < ns; ++s) {
+    type_t x = init;
+    for(int i = rseg[s]; i < seg_end(rseg, s, n); ++i)
+      x = (i == rseg[s]) ? vals[i] : op(x, vals[i]);
+    if(!(x == got[s])) return false;
+  }
+  return true;
+}
+
 int main() {
   standard_context_t context(false);
 
@@ -523,6 +552,45 @@ int main() {
     mok = mok && last.b == acc.b;
     report("transform_scan, 32-byte non-commutative op", mok);
   }
+
+  // 13. Element sizes other than 4 and 8 bytes: 1, 2 and 16. Not run on the
+  //     reference: its tile kernel lays the segment offsets out behind the
+  //     values with int-sized arithmetic
+  //     (src/moderngpu/kernel_segreduce.hxx:238-240) and faulted with an
+  //     illegal memory access on these element sizes.
+#ifndef MGPU_TEST_ON_REFERENCE
+  {
+    bool ok = check_small_type<signed char>(700001, 90000, 21,
+      maximum_t<signed char>(), (signed char)-100, context);
+    ok = ok && check_small_type<signed char>(3000000, 12, 22,
+      maximum_t<signed char>(), (signed char)-100, context);
+    report("segreduce on 1-byte values (max)", ok);
+    ok = check_small_type<short>(700001, 9000, 23, plus_t<short>(), (short)-1,
+      context);
+    ok = ok && check_small_type<short>(50000, 70000, 24, plus_t<short>(),
+      (short)-1, context);
+    report("segreduce on 2-byte values (plus)", ok);
+
+    const int n = 600000, ns = 700;
+    std::vector<int> rseg = random_segments(n, ns, 25);
+    std::vector<pair_t> vals(n);
+    for(int i = 0; i < n; ++i) vals[i] = pair_t { (double)(i % 11 - 5), (double)(i % 3) };
+    mem_t<pair_t> d_vals = to_mem(vals, context);
+    mem_t<int> d_rseg = to_mem(rseg, context);
+    mem_t<pair_t> out(ns, context);
+    segreduce(d_vals.data(), n, d_rseg.data(), ns, out.data(), pair_plus_t(),
+      pair_t { -1, -1 }, context);
+    std::vector<pair_t> got = from_mem(out);
+    ok = true;
+    for(int s = 0; s < ns && ok; ++s) {
+      pair_t x { -1, -1 };
+      for(int i = rseg[s]; i < seg_end(rseg, s, n); ++i)
+        x = (i == rseg[s]) ? vals[i] : pair_plus_t()(x, vals[i]);
+      ok = x.re == got[s].re && x.im == got[s].im;
+    }
+    report("segreduce on 16-byte values (long segments)", ok);
+  }
+#endif
 
   context.synchronize();
   if(failures) printf("FAILED %d\n", failures);
