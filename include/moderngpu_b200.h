@@ -230,6 +230,22 @@ int mgpu_b200_shard_pack(int dtype, const void* out_device,
   const int* starts_device, int num_starts, int count, void* record_device,
   void* stream);
 
+/*
+ * mgpu_b200_shard_lead writes the same 16-byte record as mgpu_b200_shard_pack,
+ * but computes the boundary partial itself from the shard's leading items
+ * (those before its first real segment start) instead of reading out[0]. It
+ * can therefore run BEFORE the shard's reduction, and the exchange of the
+ * records can overlap that reduction. `scratch_device`: at least
+ * mgpu_b200_shard_lead_scratch_bytes() bytes, 8-byte aligned, zeroed once
+ * before first use (the call leaves it ready for the next one); one scratch
+ * per stream. Built-in operators only (they commute).
+ */
+size_t mgpu_b200_shard_lead_scratch_bytes(void);
+
+int mgpu_b200_shard_lead(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* record_device,
+  void* scratch_device, void* stream);
+
 int mgpu_b200_shard_fold(int dtype, int op, const void* records_device,
   int rank, int world, void* out_device, int num_starts,
   const void* init_host, void* stream);

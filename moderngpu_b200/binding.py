@@ -118,6 +118,12 @@ def _declare_optional(lib):
     lib.mgpu_b200_shard_pack.restype = c_int
     lib.mgpu_b200_shard_pack.argtypes = [
         c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    lib.mgpu_b200_shard_lead_scratch_bytes.restype = c_size_t
+    lib.mgpu_b200_shard_lead_scratch_bytes.argtypes = []
+    lib.mgpu_b200_shard_lead.restype = c_int
+    lib.mgpu_b200_shard_lead.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_void_p]
     lib.mgpu_b200_shard_fold.restype = c_int
     lib.mgpu_b200_shard_fold.argtypes = [
         c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,

@@ -4,12 +4,17 @@ evenly across ranks, one 16-byte boundary record exchanged per rank.
 The reference is single-device (src/moderngpu/context.hxx:85,109-110 knows one
 stream on the current device); this layer is new. Data path per rank:
 
-  1. mgpu_b200_segreduce on the shard (items, shard-local start table);
-  2. mgpu_b200_shard_pack: boundary partial + flags -> 16-byte record;
-  3. torch.distributed all_gather of the records (16 bytes per rank -- the
-     only exchange; NVLink carries it when the backend is NCCL);
+  1. mgpu_b200_shard_lead: fold of the shard's leading items (those before
+     its first segment start) + flags -> 16-byte boundary record;
+  2. torch.distributed all_gather of the records (16 bytes per rank -- the
+     only exchange; NVLink carries it when the backend is NCCL), started
+     asynchronously so that it overlaps step 3;
+  3. mgpu_b200_segreduce on the shard (items, shard-local start table);
   4. mgpu_b200_shard_fold: the rank that owns a straddling segment folds the
      following ranks' partials into its last output, in rank order.
+
+With overlap=False the record is taken from the reduction's own first output
+instead (mgpu_b200_shard_pack) and the exchange follows the reduction.
 
 Shard-local start table: entry 0 is always 0 and stands for the segment
 carried in from the previous rank; the remaining entries are the local offsets
@@ -89,8 +94,23 @@ def fold_plan(flags, rank):
     return take
 
 
+_lead_scratch = {}
+
+
+def lead_scratch(dev):
+    """Zeroed scratch of mgpu_b200_shard_lead, one per device (calls on one
+    stream follow one another, and every call leaves it zeroed)."""
+    key = (dev.type, dev.index)
+    if key not in _lead_scratch:
+        lib = binding.load_library()
+        size = lib.mgpu_b200_shard_lead_scratch_bytes()
+        _lead_scratch[key] = torch.zeros((size + 7) // 8, dtype=torch.int64,
+                                         device=dev)
+    return _lead_scratch[key]
+
+
 def sharded_segreduce(values, table, op="plus", init=0, group=None,
-                      records=None):
+                      records=None, overlap=True):
     """Reduce this rank's shard and fold boundary partials across ranks.
 
     values: this rank's items (CUDA tensor); table: its shard-local start
@@ -103,13 +123,14 @@ def sharded_segreduce(values, table, op="plus", init=0, group=None,
             "sharded_segreduce runs on CUDA tensors only (no CPU fallback)")
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    return _sharded_cuda(values, table, op, init, group, rank, world, records)
+    return _sharded_cuda(values, table, op, init, group, rank, world, records,
+                         overlap)
 
 
-def _sharded_cuda(values, table, op, init, group, rank, world, records):
+def _sharded_cuda(values, table, op, init, group, rank, world, records,
+                  overlap):
     lib = binding.load_library()
     dev = values.device
-    out = binding.segreduce(values, table, op=op, init=init)
     dtype = binding._DTYPES[values.dtype]
     stream = binding._stream(dev)
     mine = torch.empty(RECORD_BYTES, dtype=torch.uint8, device=dev)
@@ -117,12 +138,26 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records):
         records = torch.empty(world * RECORD_BYTES, dtype=torch.uint8,
                               device=dev)
     with torch.cuda.device(dev):
-        binding._check(lib.mgpu_b200_shard_pack(
-            dtype, out.data_ptr(), table.data_ptr(), table.numel(),
-            values.numel(), mine.data_ptr(), stream))
-        if world > 1:
-            dist.all_gather_into_tensor(records, mine, group=group)
-        else:
+        pending = None
+        if overlap:
+            binding._check(lib.mgpu_b200_shard_lead(
+                dtype, binding._OPS[op], values.data_ptr(), values.numel(),
+                table.data_ptr(), table.numel(), mine.data_ptr(),
+                lead_scratch(dev).data_ptr(), stream))
+            if world > 1:
+                pending = dist.all_gather_into_tensor(records, mine,
+                                                      group=group,
+                                                      async_op=True)
+        out = binding.segreduce(values, table, op=op, init=init)
+        if not overlap:
+            binding._check(lib.mgpu_b200_shard_pack(
+                dtype, out.data_ptr(), table.data_ptr(), table.numel(),
+                values.numel(), mine.data_ptr(), stream))
+            if world > 1:
+                dist.all_gather_into_tensor(records, mine, group=group)
+        if pending is not None:
+            pending.wait()
+        if world == 1:
             records[:RECORD_BYTES].copy_(mine)
         init_c = binding._CTYPES[values.dtype](init)
         binding._check(lib.mgpu_b200_shard_fold(
@@ -132,7 +167,7 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records):
 
 
 def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
-                            workspace=None):
+                            workspace=None, overlap=True):
     """Several consecutive shards per rank (CUDA tensors only).
 
     shards: list of (values, table) pairs held by this rank, in array order;
@@ -154,17 +189,33 @@ def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
                           device=dev)
     results = []
     with torch.cuda.device(dev):
+        pending = None
+        if overlap:
+            for j, (values, table) in enumerate(shards):
+                binding._check(lib.mgpu_b200_shard_lead(
+                    dtype, binding._OPS[op], values.data_ptr(),
+                    values.numel(), table.data_ptr(), table.numel(),
+                    mine.data_ptr() + j * RECORD_BYTES,
+                    lead_scratch(dev).data_ptr(), stream))
+            if world > 1:
+                pending = dist.all_gather_into_tensor(records, mine,
+                                                      group=group,
+                                                      async_op=True)
         for j, (values, table) in enumerate(shards):
             out = binding.segreduce(values, table, op=op, init=init,
                                     out=None if outs is None else outs[j],
                                     workspace=workspace)
-            binding._check(lib.mgpu_b200_shard_pack(
-                dtype, out.data_ptr(), table.data_ptr(), table.numel(),
-                values.numel(), mine.data_ptr() + j * RECORD_BYTES, stream))
+            if not overlap:
+                binding._check(lib.mgpu_b200_shard_pack(
+                    dtype, out.data_ptr(), table.data_ptr(), table.numel(),
+                    values.numel(), mine.data_ptr() + j * RECORD_BYTES,
+                    stream))
             results.append(out)
-        if world > 1:
+        if world > 1 and not overlap:
             dist.all_gather_into_tensor(records, mine, group=group)
-        else:
+        if pending is not None:
+            pending.wait()
+        if world == 1:
             records.copy_(mine)
         init_c = binding._CTYPES[shards[0][0].dtype](init)
         for j, (values, table) in enumerate(shards):

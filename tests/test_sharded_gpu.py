@@ -1,6 +1,8 @@
 """Multi-GPU segmented reduction on real GPUs (needs at least 2): one process
 per GPU over NCCL, shard-local reduction by the library's kernels, boundary
-records all-gathered, owner-side fold by mgpu_b200_shard_fold. The assembled
+records (from the shard's leading items, exchanged while the reduction runs;
+or from the reduction's first output) all-gathered, owner-side fold by
+mgpu_b200_shard_fold. The assembled
 result must equal the oracle's reduction of the whole array."""
 import os
 import socket
@@ -39,7 +41,7 @@ def make_problem(kind, dtype):
     return values, seg
 
 
-def worker(rank, world, port, kind, dtype_name, op, queue):
+def worker(rank, world, port, kind, dtype_name, op, overlap, queue):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
@@ -52,7 +54,7 @@ def worker(rank, world, port, kind, dtype_name, op, queue):
         begin, end, first, table = sharded.shard_table(seg, values.size, rank, world)
         out = sharded.sharded_segreduce(
             torch.from_numpy(values[begin:end].copy()).cuda(),
-            torch.from_numpy(table).cuda(), op=op, init=-7)
+            torch.from_numpy(table).cuda(), op=op, init=-7, overlap=overlap)
         torch.cuda.synchronize()
         pieces = [None] * world
         dist.all_gather_object(pieces, (first, out.cpu().numpy()[1:].tolist()))
@@ -62,19 +64,20 @@ def worker(rank, world, port, kind, dtype_name, op, queue):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("kind,dtype,op", [
-    ("lognormal", "float64", "max"), ("lognormal", "int64", "plus"),
-    ("few_long", "int32", "plus"), ("one", "float64", "min"),
-    ("lognormal", "float64", "plus"),
+@pytest.mark.parametrize("kind,dtype,op,overlap", [
+    ("lognormal", "float64", "max", True), ("lognormal", "int64", "plus", True),
+    ("few_long", "int32", "plus", True), ("one", "float64", "min", True),
+    ("lognormal", "float64", "plus", True), ("lognormal", "int64", "plus", False),
+    ("few_long", "int32", "plus", False),
 ])
-def test_sharded_matches_oracle(oracle, kind, dtype, op):
+def test_sharded_matches_oracle(oracle, kind, dtype, op, overlap):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = free_port()
-    procs = [ctx.Process(target=worker, args=(r, world, port, kind, dtype, op, queue))
+    procs = [ctx.Process(target=worker, args=(r, world, port, kind, dtype, op, overlap, queue))
              for r in range(world)]
     for p in procs:
         p.start()
@@ -95,11 +98,12 @@ def test_sharded_matches_oracle(oracle, kind, dtype, op):
         assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("overlap", [True, False])
 @pytest.mark.parametrize("kind,dtype,op", [
     ("lognormal", "float64", "max"), ("few_long", "int64", "plus"),
     ("one", "int32", "plus"),
 ])
-def test_several_shards_on_one_gpu(mgpu, oracle, kind, dtype, op):
+def test_several_shards_on_one_gpu(mgpu, oracle, kind, dtype, op, overlap):
     """The array cut into 5 shards that one GPU reduces one after the other
     (how an array beyond the 2^31 index limit of a single call is handled);
     the chain of boundary records is folded exactly as across GPUs."""
@@ -111,10 +115,48 @@ def test_several_shards_on_one_gpu(mgpu, oracle, kind, dtype, op):
         shards.append((torch.from_numpy(values[begin:end].copy()).cuda(),
                        torch.from_numpy(table).cuda()))
         firsts.append(first)
-    outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7)
+    outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7,
+                                           overlap=overlap)
     got = np.zeros(seg.size, dtype=np.float64)
     for first, out in zip(firsts, outs):
         vals = out.cpu().numpy()[1:]
         got[first:first + vals.size] = vals
     want = oracle.segreduce(values, seg.astype(np.int32), op=op, init=-7)
     assert np.array_equal(got, want.astype(np.float64))
+
+
+@pytest.mark.parametrize("dtype,op", [("int32", "plus"), ("int64", "min"),
+                                      ("float32", "max"), ("float64", "min")])
+@pytest.mark.parametrize("lead", [0, 1, 63, 64, 65, 1000, 8192, 8193, 300_001, 1_000_000])
+def test_lead_record_equals_pack_record(mgpu, dtype, op, lead):
+    """mgpu_b200_shard_lead (from the items) and mgpu_b200_shard_pack (from the
+    reduction's first output) write the same record; called twice to check
+    that the scratch is left ready."""
+    import ctypes
+    from moderngpu_b200 import binding
+    lib = binding.load_library()
+    rng = np.random.default_rng(lead + 5)
+    count = 1_000_000
+    values = rng.integers(-10**6, 10**6, size=count).astype(dtype)
+    if lead < count:
+        table = np.array([0, lead, min(lead + 17, count), count], dtype=np.int32)
+    else:
+        table = np.array([0], dtype=np.int32)
+    v = torch.from_numpy(values).cuda()
+    t = torch.from_numpy(table).cuda()
+    out = mgpu.segreduce(v, t, op=op, init=3)
+    recs = torch.zeros(3, 2, dtype=torch.int64, device="cuda")
+    stream = binding._stream(v.device)
+    code = binding._DTYPES[v.dtype]
+    binding._check(lib.mgpu_b200_shard_pack(
+        code, out.data_ptr(), t.data_ptr(), t.numel(), count,
+        recs[0].data_ptr(), stream))
+    for k in (1, 2):
+        binding._check(lib.mgpu_b200_shard_lead(
+            code, binding._OPS[op], v.data_ptr(), count, t.data_ptr(),
+            t.numel(), recs[k].data_ptr(),
+            sharded.lead_scratch(v.device).data_ptr(), stream))
+    got = recs.cpu().numpy()
+    assert got[0, 1] == got[1, 1] == got[2, 1]            # flags
+    if lead > 0:
+        assert got[0, 0] == got[1, 0] == got[2, 0]        # the partial's bits
