@@ -204,14 +204,17 @@ def run_reference_cpu(args, rank, world):
     emit(line)
 
 
-def workload_config(n_gpus):
+def workload_config(n_gpus, exchange="p2p"):
+    how = ("stored peer-to-peer over NVLink into the owning GPU's mailbox, "
+           "no collective" if exchange == "p2p" else "NCCL all-gather")
     return {
         "workload": "config 2: fp32 plus-segreduce, %d items uniform in "
                     "[-1,1), %d segments, geometric lengths mean 32 with 5%% "
                     "empty, init 0 (per GPU)" % (COUNT, NUM_SEGMENTS),
         "items_per_gpu": COUNT, "segments_per_gpu": NUM_SEGMENTS,
         "sharding": "item range cut evenly over %d GPU(s); one 16-byte "
-                    "boundary record per GPU exchanged per step" % n_gpus,
+                    "boundary record per GPU exchanged per step (%s)"
+                    % (n_gpus, how if n_gpus > 1 else "none needed"),
         "l2": "inputs are %.2f GB per GPU, larger than the 126 MB L2; no "
               "flush between steps" % ((COUNT * 4 + NUM_SEGMENTS * 8) / 1e9),
     }
@@ -324,9 +327,16 @@ def run_ours(args, rank, world, local_rank):
     records = torch.empty(world * sharded.RECORD_BYTES, dtype=torch.uint8,
                           device=device)
 
+    mailbox = None
+    if world > 1 and args.exchange == "p2p":
+        mailbox = sharded.Mailbox()
+
     def step():
         if world == 1:
             mgpu.segreduce(values, seg, op="plus", init=0.0, out=out)
+        elif mailbox is not None:
+            sharded.sharded_segreduce(values, table, op="plus", init=0.0,
+                                      mailbox=mailbox)
         else:
             sharded.sharded_segreduce(values, table, op="plus", init=0.0,
                                       records=records)
@@ -335,6 +345,7 @@ def run_ours(args, rank, world, local_rank):
         step()
     torch.cuda.synchronize()
     assert mgpu.workspace_status() == 0, "device-side status reported failure"
+    assert mailbox is None or mailbox.status() == 0, "mailbox wait timed out"
 
     if world > 1:
         dist.barrier()
@@ -438,7 +449,7 @@ def run_ours(args, rank, world, local_rank):
             "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": workload_config(world),
+            "data": "synthetic", "config": workload_config(world, args.exchange),
             "hbm_gbs_per_gpu": workloads.segreduce_bytes(
                 COUNT, NUM_SEGMENTS, 4) / (ms_per_step * 1e-3) / 1e9,
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
@@ -446,6 +457,8 @@ def run_ours(args, rank, world, local_rank):
             "clocks": clocks,
         }
         emit(line)
+    if mailbox is not None:
+        mailbox.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -510,10 +523,12 @@ def run_other_config(args, rank, world, local_rank):
             nbytes += workloads.segreduce_bytes(count, table.numel(), 8)
         outs = [torch.empty(t.numel(), dtype=torch.float64, device=device)
                 for _, t in shards]
+        box = (sharded.Mailbox(shards_per_gpu=per_rank)
+               if args.exchange == "p2p" else None)
         for op, init in (("max", -1e300), ("plus", 0.0)):
             steps["fp64 %s, 2^32 items in 8 shards" % op] = (
                 lambda op=op, init=init: sharded.sharded_segreduce_multi(
-                    shards, op=op, init=init, outs=outs),
+                    shards, op=op, init=init, outs=outs, mailbox=box),
                 per_rank * count, nbytes)
     peak, peak_kind = measured_peak()
     results = []
@@ -542,11 +557,14 @@ def run_other_config(args, rank, world, local_rank):
                         "hbm_gbs_per_gpu": gbs,
                         "frac_of_%s_peak" % peak_kind: gbs / peak})
     assert mgpu.workspace_status() == 0
+    if cfg == "c5" and box is not None:
+        assert box.status() == 0
+        box.close()
     if rank == 0:
         emit({"config": cfg, "n_gpus": world, "steps": args.steps,
               "note": "includes every launch of a step (partitioner + "
-                      "kernel, plus record pack / all-gather / fold when "
-                      "n_gpus > 1)",
+                      "kernel, plus the boundary-record post / collect "
+                      "kernels of the multi-GPU layer)",
               "results": results})
     if world > 1:
         dist.destroy_process_group()
@@ -574,6 +592,10 @@ def main():
                         choices=["c1", "c2", "c3", "c4", "c5", "scan"],
                         help="c2 (default) is the headline line; the others "
                              "print a shorter secondary line")
+    parser.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],
+                        help="multi-GPU boundary records: peer-to-peer "
+                             "stores into mailboxes (default) or an NCCL "
+                             "all-gather")
     parser.add_argument("--impl", default="ours",
                         choices=["ours", "reference", "reference-cuda"])
     args = parser.parse_args()

@@ -246,6 +246,54 @@ int mgpu_b200_shard_lead(int dtype, int op, const void* input_device,
   int count, const int* starts_device, int num_starts, void* record_device,
   void* scratch_device, void* stream);
 
+/*
+ * Peer-to-peer exchange of the boundary records (no collective library).
+ *
+ * Every GPU owns one mailbox: a block of device memory that the other GPUs of
+ * the box map into their address space (CUDA IPC) and write into over NVLink.
+ * mgpu_b200_mailbox_create allocates and zeroes it on the current device and
+ * returns a 64-byte handle; the caller hands the handle to the other
+ * processes by whatever means it has, and each of them maps it with
+ * mgpu_b200_mailbox_open (close with mgpu_b200_mailbox_close before the
+ * owner destroys it). A process must not open its own handle; it uses the
+ * pointer mgpu_b200_mailbox_create returned.
+ *
+ * The array is a chain of num_shards consecutive shards (at most 64),
+ * shards_per_gpu of them on each GPU in order; peers_device is a DEVICE array
+ * of num_shards / shards_per_gpu mailbox pointers, indexed by GPU, this GPU's
+ * own mailbox at its own index. `step` counts the calls: 1 for the first
+ * step, one more for each following step, the same on every GPU.
+ *
+ * mgpu_b200_shard_post reduces the shard's leading items (as
+ * mgpu_b200_shard_lead) and stores the record into the mailbox of every GPU
+ * that holds this or an earlier shard. mgpu_b200_shard_collect, enqueued
+ * after the shard's mgpu_b200_segreduce, waits in THIS GPU's memory for the
+ * records of the following shards and folds them into out[num_starts - 1]
+ * (as mgpu_b200_shard_fold), then releases the records' slots. Slots are
+ * reused after 64 steps; a GPU that runs 64 steps ahead of a reader waits
+ * for it. Every wait is bounded: after timeout_ns (0 = 10 s) the kernel
+ * gives up, leaves the output untouched and sets the mailbox's status word,
+ * which mgpu_b200_mailbox_status reads back (0 fine, 3 = a record did not
+ * arrive, 4 = a slot was not released). One mailbox serves one stream.
+ */
+size_t mgpu_b200_mailbox_bytes(void);
+int mgpu_b200_mailbox_create(void** mailbox_device, void* handle_out);
+int mgpu_b200_mailbox_open(const void* handle_in, void** peer_device);
+int mgpu_b200_mailbox_close(void* peer_device);
+int mgpu_b200_mailbox_destroy(void* mailbox_device);
+int mgpu_b200_mailbox_status(const void* mailbox_device, void* stream,
+  int* status_host);
+
+int mgpu_b200_shard_post(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* mailbox_device,
+  const void* const* peers_device, int shard, int num_shards,
+  int shards_per_gpu, unsigned step, uint64_t timeout_ns, void* stream);
+
+int mgpu_b200_shard_collect(int dtype, int op, void* mailbox_device,
+  const void* const* peers_device, int shard, int num_shards,
+  int shards_per_gpu, unsigned step, void* out_device, int num_starts,
+  const void* init_host, uint64_t timeout_ns, void* stream);
+
 int mgpu_b200_shard_fold(int dtype, int op, const void* records_device,
   int rank, int world, void* out_device, int num_starts,
   const void* init_host, void* stream);

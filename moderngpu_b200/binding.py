@@ -124,6 +124,29 @@ def _declare_optional(lib):
     lib.mgpu_b200_shard_lead.argtypes = [
         c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
         c_void_p]
+    lib.mgpu_b200_mailbox_bytes.restype = c_size_t
+    lib.mgpu_b200_mailbox_bytes.argtypes = []
+    lib.mgpu_b200_mailbox_create.restype = c_int
+    lib.mgpu_b200_mailbox_create.argtypes = [ctypes.POINTER(c_void_p),
+                                             c_void_p]
+    lib.mgpu_b200_mailbox_open.restype = c_int
+    lib.mgpu_b200_mailbox_open.argtypes = [c_void_p,
+                                           ctypes.POINTER(c_void_p)]
+    lib.mgpu_b200_mailbox_close.restype = c_int
+    lib.mgpu_b200_mailbox_close.argtypes = [c_void_p]
+    lib.mgpu_b200_mailbox_destroy.restype = c_int
+    lib.mgpu_b200_mailbox_destroy.argtypes = [c_void_p]
+    lib.mgpu_b200_mailbox_status.restype = c_int
+    lib.mgpu_b200_mailbox_status.argtypes = [c_void_p, c_void_p,
+                                             ctypes.POINTER(c_int)]
+    lib.mgpu_b200_shard_post.restype = c_int
+    lib.mgpu_b200_shard_post.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_int, c_int, c_int, ctypes.c_uint, ctypes.c_uint64, c_void_p]
+    lib.mgpu_b200_shard_collect.restype = c_int
+    lib.mgpu_b200_shard_collect.argtypes = [
+        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, ctypes.c_uint,
+        c_void_p, c_int, c_void_p, ctypes.c_uint64, c_void_p]
     lib.mgpu_b200_shard_fold.restype = c_int
     lib.mgpu_b200_shard_fold.argtypes = [
         c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,

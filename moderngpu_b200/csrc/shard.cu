@@ -24,8 +24,104 @@ enum : uint32_t {
 struct shard_record_t {
   unsigned long long value;   // the partial's bits, zero-padded to 8 bytes
   uint32_t flags;
-  uint32_t pad;
+  uint32_t seq;               // mailbox only: the step the record belongs to
 };
+
+// Mailbox: one block of device memory per GPU that the other GPUs of the box
+// map (CUDA IPC) and write into over NVLink. Fixed layout:
+//   [0, 256)        status word (0 = fine, 3 = a record did not arrive in
+//                   time, 4 = a ring slot was not released in time)
+//   [256, 1280)     scratch of the leading-items reduction
+//   [1280, 9472)    acks: shard v's last finished step, one 128-byte line each,
+//                   written by the GPU that holds shard v
+//   [9472, ...)     slots[shard][step % ring]: 32-byte records written by the
+//                   GPU that holds the shard
+// A record travels as three 8-byte words that each carry the step number in
+// their upper half next to 32 bits of payload (value low, value high, flags):
+// every word is one atomic store, so the reader needs no fence -- it polls
+// its OWN memory until all three words show the step it waits for. No kernel
+// ever polls another GPU's memory.
+enum {
+  mailbox_ring = 64, mailbox_max_shards = 64,
+  mailbox_scratch_offset = 256, mailbox_ack_offset = 1280,
+  mailbox_slot_offset = mailbox_ack_offset + 128 * mailbox_max_shards,
+  mailbox_slot_bytes = 32,
+  mailbox_used_bytes = mailbox_slot_offset +
+    mailbox_slot_bytes * mailbox_ring * mailbox_max_shards,
+  mailbox_alloc_bytes = 2 << 20,   // a whole allocation block of its own
+  status_record_timeout = 3, status_slot_timeout = 4
+};
+
+struct mailbox_t {
+  char* base;
+  __device__ uint32_t* status() const { return (uint32_t*)base; }
+  __device__ volatile uint32_t* ack(int shard) const {
+    return (volatile uint32_t*)(base + mailbox_ack_offset + 128 * shard);
+  }
+  __device__ volatile unsigned long long* slot(int shard, uint32_t step) const {
+    return (volatile unsigned long long*)(base + mailbox_slot_offset +
+      mailbox_slot_bytes * (shard * mailbox_ring + step % mailbox_ring));
+  }
+};
+
+// What a posting / collecting kernel needs to know about the chain of shards.
+// peers[p] is GPU p's mailbox as mapped into this GPU's address space (this
+// GPU's own mailbox at its own index). Shard v lives on GPU v / per_gpu.
+struct chain_t {
+  char* const* peers;       // null: no mailbox, write `record` only
+  int shard, num_shards, per_gpu;
+  uint32_t step;
+  unsigned long long timeout_ns;
+};
+
+__device__ __forceinline__ unsigned long long timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits, for at most timeout_ns, until this GPU's copy of the record of
+// (shard, step) is complete. Returns false when time ran out.
+__device__ bool wait_record(const mailbox_t& box, int shard, uint32_t step,
+  unsigned long long timeout_ns, shard_record_t& got) {
+  volatile unsigned long long* word = box.slot(shard, step);
+  unsigned long long begin = 0;
+  for(unsigned spin = 0; ; ++spin) {
+    unsigned long long w0 = word[0], w1 = word[1], w2 = word[2];
+    if((uint32_t)(w0 >> 32) == step && (uint32_t)(w1 >> 32) == step &&
+      (uint32_t)(w2 >> 32) == step) {
+      got.value = (w0 & 0xffffffffull) | (w1 << 32);
+      got.flags = (uint32_t)w2;
+      got.seq = step;
+      return true;
+    }
+    if(0 == (spin & 63)) {
+      unsigned long long now = timer_ns();
+      if(!begin) begin = now;
+      else if(now - begin > timeout_ns) return false;
+    }
+  }
+}
+
+// Waits until every shard held by GPU `gpu` has finished step `step - ring`,
+// i.e. until the ring slot about to be overwritten there is no longer read.
+__device__ bool wait_slot_free(const mailbox_t& box, const chain_t& chain,
+  int gpu) {
+  if(chain.step <= (uint32_t)mailbox_ring) return true;
+  const uint32_t need = chain.step - mailbox_ring;
+  const int v_end = min((gpu + 1) * chain.per_gpu, chain.num_shards);
+  unsigned long long begin = 0;
+  for(int v = gpu * chain.per_gpu; v < v_end; ++v) {
+    for(unsigned spin = 0; ; ++spin) {
+      if((int)(*box.ack(v) - need) >= 0) break;
+      if(0 == (spin & 63)) {
+        unsigned long long now = timer_ns();
+        if(!begin) begin = now;
+        else if(now - begin > chain.timeout_ns) return false;
+      }
+    }
+  }
+  return true;
+}
 
 template<typename type_t>
 __global__ void shard_pack_k(const type_t* out, const int* starts,
@@ -42,7 +138,7 @@ __global__ void shard_pack_k(const type_t* out, const int* starts,
   memcpy(&bits, &v, sizeof(type_t));
   record->value = bits;
   record->flags = flags;
-  record->pad = 0;
+  record->seq = 0;
 }
 
 template<typename type_t>
@@ -129,25 +225,49 @@ __device__ void lead_cta_fold(int op, type_t& acc, bool& has,
   __syncthreads();
 }
 
+// Called by every thread of the CTA that holds the shard's total (in thread
+// 0): writes the record locally and, with a mailbox, into the mailbox of every
+// GPU that holds this shard or an earlier one -- thread p serves GPU p.
 template<typename type_t>
-__device__ void lead_write_record(shard_record_t* record, type_t total,
-  int lead, bool real, const int* starts, int num_starts, int count) {
-  uint32_t flags = 0;
-  if(lead > 0) flags |= shard_has_partial;
-  if(real) flags |= shard_has_start;
-  if(real && starts[num_starts - 1] >= count) flags |= shard_last_empty;
-  unsigned long long bits = 0;
-  memcpy(&bits, &total, sizeof(type_t));
-  record->value = bits;
-  record->flags = flags;
-  record->pad = 0;
+__device__ void lead_finish(shard_record_t* record, type_t total, int lead,
+  bool real, const int* starts, int num_starts, int count,
+  const chain_t& chain, char* mailbox) {
+  __shared__ shard_record_t posted;
+  const int tid = (int)threadIdx.x;
+  if(0 == tid) {
+    uint32_t flags = 0;
+    if(lead > 0) flags |= shard_has_partial;
+    if(real) flags |= shard_has_start;
+    if(real && starts[num_starts - 1] >= count) flags |= shard_last_empty;
+    unsigned long long bits = 0;
+    memcpy(&bits, &total, sizeof(type_t));
+    posted.value = bits;
+    posted.flags = flags;
+    posted.seq = chain.step;
+    if(record) *record = posted;
+  }
+  if(!chain.peers) return;
+  __syncthreads();
+  const int last_gpu = chain.shard / chain.per_gpu;
+  if(tid <= last_gpu) {
+    mailbox_t mine = { mailbox };
+    if(wait_slot_free(mine, chain, tid)) {
+      mailbox_t theirs = { chain.peers[tid] };
+      volatile unsigned long long* word = theirs.slot(chain.shard, chain.step);
+      const unsigned long long tag = (unsigned long long)chain.step << 32;
+      word[0] = (posted.value & 0xffffffffull) | tag;
+      word[1] = (posted.value >> 32) | tag;
+      word[2] = (unsigned long long)posted.flags | tag;
+    } else
+      atomicMax(mine.status(), (uint32_t)status_slot_timeout);
+  }
 }
 
 template<typename type_t>
 __global__ void __launch_bounds__(lead_threads)
 shard_lead_k(const type_t* input, const int* starts, int num_starts, int count,
   int op, shard_record_t* record, unsigned long long* chunk_value,
-  uint32_t* chunk_has, uint32_t* ticket) {
+  uint32_t* chunk_has, uint32_t* ticket, chain_t chain, char* mailbox) {
   __shared__ type_t warp_value[lead_threads / 32];
   __shared__ int warp_has[lead_threads / 32];
   __shared__ bool last_cta;
@@ -175,8 +295,8 @@ shard_lead_k(const type_t* input, const int* starts, int num_starts, int count,
   }
   lead_cta_fold(op, acc, has, warp_value, warp_has);
   if(alone) {
-    if(0 == tid)
-      lead_write_record(record, acc, lead, real, starts, num_starts, count);
+    lead_finish(record, acc, lead, real, starts, num_starts, count, chain,
+      mailbox);
     return;
   }
 
@@ -198,11 +318,92 @@ shard_lead_k(const type_t* input, const int* starts, int num_starts, int count,
     memcpy(&acc, &bits, sizeof(type_t));
   }
   lead_cta_fold(op, acc, has, warp_value, warp_has);
-  if(0 == tid) {
-    lead_write_record(record, acc, lead, real, starts, num_starts, count);
-    *ticket = 0;
+  if(0 == tid) *ticket = 0;
+  lead_finish(record, acc, lead, real, starts, num_starts, count, chain,
+    mailbox);
+}
+
+// The owner's side: shard `chain.shard` folds the partials of the following
+// shards into its last output (same rule as shard_fold_k), reading the records
+// from this GPU's own mailbox as they arrive, then tells the GPUs that hold
+// later shards that it is done with the step.
+template<typename type_t>
+__global__ void shard_collect_k(char* mailbox, chain_t chain, int op,
+  type_t* out, int num_starts, type_t init) {
+  const int lane = (int)threadIdx.x;
+  const unsigned full = 0xffffffffu;
+  mailbox_t box = { mailbox };
+
+  // Everything the warp may need is requested at once: lane l looks (once,
+  // without waiting) at the record of shard `shard + l`, lane 0 also at the
+  // output it may update, and every lane at the mailbox it will ack to.
+  const int first_gpu = chain.shard / chain.per_gpu;
+  const int gpus = (chain.num_shards + chain.per_gpu - 1) / chain.per_gpu;
+  char* ack_to = first_gpu + lane < gpus ? chain.peers[first_gpu + lane] : nullptr;
+  shard_record_t seen = shard_record_t();
+  bool seen_ok = false;
+  if(chain.shard + lane < chain.num_shards) {
+    volatile unsigned long long* word = box.slot(chain.shard + lane, chain.step);
+    unsigned long long w0 = word[0], w1 = word[1], w2 = word[2];
+    seen_ok = (uint32_t)(w0 >> 32) == chain.step &&
+      (uint32_t)(w1 >> 32) == chain.step && (uint32_t)(w2 >> 32) == chain.step;
+    seen.value = (w0 & 0xffffffffull) | (w1 << 32);
+    seen.flags = (uint32_t)w2;
+  }
+  type_t last = type_t();
+  if(0 == lane) last = out[num_starts - 1];
+
+  // The warp walks the chain together; a record that had not arrived at the
+  // first look is waited for (bounded) by lane 0.
+  bool ok = true, have = false, stop = false;
+  type_t acc = init;
+  uint32_t mine = 0;
+  for(int i = 0; ok && !stop && chain.shard + i < chain.num_shards; ++i) {
+    shard_record_t r = shard_record_t();
+    bool got = false;
+    if(i < 32) {
+      got = __shfl_sync(full, (int)seen_ok, i);
+      r.value = __shfl_sync(full, seen.value, i);
+      r.flags = __shfl_sync(full, seen.flags, i);
+    }
+    if(!got) {
+      int fine = 0;
+      if(0 == lane)
+        fine = wait_record(box, chain.shard + i, chain.step, chain.timeout_ns, r);
+      ok = __shfl_sync(full, fine, 0);
+      r.value = __shfl_sync(full, r.value, 0);
+      r.flags = __shfl_sync(full, r.flags, 0);
+      if(!ok) break;
+    }
+    if(0 == i) {
+      mine = r.flags;
+      stop = !(mine & shard_has_start);      // owns nothing
+      continue;
+    }
+    if(r.flags & shard_has_partial) {
+      type_t x;
+      memcpy(&x, &r.value, sizeof(type_t));
+      acc = have ? apply(op, acc, x) : x;
+      have = true;
+    }
+    stop = 0 != (r.flags & shard_has_start);
+  }
+  if(0 == lane) {
+    if(!ok) atomicMax(box.status(), (uint32_t)status_record_timeout);
+    else if(have)
+      out[num_starts - 1] = (mine & shard_last_empty) ? acc : apply(op, last, acc);
+  }
+  // Done reading this step's records (also after a timeout: the writers must
+  // not be held up by a reader that has given up).
+  if(ack_to) { mailbox_t theirs = { ack_to }; *theirs.ack(chain.shard) = chain.step; }
+  for(int p = first_gpu + 32 + lane; p < gpus; p += 32) {
+    mailbox_t theirs = { chain.peers[p] };
+    *theirs.ack(chain.shard) = chain.step;
   }
 }
+
+// How long a kernel waits for another GPU's record or ack before it gives up.
+const unsigned long long default_mailbox_wait_ns = 10000000000ull;
 
 inline int code_of(cudaError_t e) {
   return cudaSuccess == e ? MGPU_B200_OK : MGPU_B200_E_CUDA + (int)e;
@@ -231,16 +432,139 @@ int mgpu_b200_shard_lead(int dtype, int op, const void* input_device,
   switch(dtype) {
     case MGPU_B200_F32: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
       (const float*)input_device, starts_device, num_starts, count, op, rec,
-      values, has, ticket); break;
+      values, has, ticket, chain_t(), nullptr); break;
     case MGPU_B200_F64: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
       (const double*)input_device, starts_device, num_starts, count, op, rec,
-      values, has, ticket); break;
+      values, has, ticket, chain_t(), nullptr); break;
     case MGPU_B200_I32: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
       (const int*)input_device, starts_device, num_starts, count, op, rec,
-      values, has, ticket); break;
+      values, has, ticket, chain_t(), nullptr); break;
     case MGPU_B200_I64: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
       (const long long*)input_device, starts_device, num_starts, count, op,
-      rec, values, has, ticket); break;
+      rec, values, has, ticket, chain_t(), nullptr); break;
+    default: return MGPU_B200_E_UNSUPPORTED;
+  }
+  return code_of(cudaGetLastError());
+}
+
+size_t mgpu_b200_mailbox_bytes(void) { return mailbox_alloc_bytes; }
+
+int mgpu_b200_mailbox_create(void** mailbox_device, void* handle_out) {
+  if(!mailbox_device || !handle_out) return MGPU_B200_E_INVALID;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  static_assert(mailbox_used_bytes <= mailbox_alloc_bytes, "mailbox size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, mailbox_alloc_bytes);
+  if(cudaSuccess != e) return code_of(e);
+  e = cudaMemset(p, 0, mailbox_alloc_bytes);
+  if(cudaSuccess == e) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t handle;
+  if(cudaSuccess == e) e = cudaIpcGetMemHandle(&handle, p);
+  if(cudaSuccess != e) { cudaFree(p); return code_of(e); }
+  memcpy(handle_out, &handle, sizeof(handle));
+  *mailbox_device = p;
+  return MGPU_B200_OK;
+}
+
+int mgpu_b200_mailbox_open(const void* handle_in, void** peer_device) {
+  if(!handle_in || !peer_device) return MGPU_B200_E_INVALID;
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, handle_in, sizeof(handle));
+  return code_of(cudaIpcOpenMemHandle(peer_device, handle,
+    cudaIpcMemLazyEnablePeerAccess));
+}
+
+int mgpu_b200_mailbox_close(void* peer_device) {
+  if(!peer_device) return MGPU_B200_E_INVALID;
+  return code_of(cudaIpcCloseMemHandle(peer_device));
+}
+
+int mgpu_b200_mailbox_destroy(void* mailbox_device) {
+  if(!mailbox_device) return MGPU_B200_E_INVALID;
+  return code_of(cudaFree(mailbox_device));
+}
+
+int mgpu_b200_mailbox_status(const void* mailbox_device, void* stream,
+  int* status_host) {
+  if(!mailbox_device || !status_host) return MGPU_B200_E_INVALID;
+  uint32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, mailbox_device, 4,
+    cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if(cudaSuccess == e) e = cudaStreamSynchronize((cudaStream_t)stream);
+  *status_host = (int)word;
+  return code_of(e);
+}
+
+static bool chain_ok(const void* mailbox, const void* peers, int shard,
+  int num_shards, int per_gpu, unsigned step) {
+  return mailbox && peers && per_gpu >= 1 && num_shards >= 1 &&
+    num_shards <= mailbox_max_shards && 0 == num_shards % per_gpu &&
+    num_shards / per_gpu <= lead_threads &&
+    shard >= 0 && shard < num_shards && step >= 1;
+}
+
+int mgpu_b200_shard_post(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* mailbox_device,
+  const void* const* peers_device, int shard, int num_shards,
+  int shards_per_gpu, unsigned step, uint64_t timeout_ns, void* stream) {
+  if(!starts_device || num_starts < 1 || count < 0 ||
+    (count && !input_device) ||
+    !chain_ok(mailbox_device, peers_device, shard, num_shards, shards_per_gpu,
+      step))
+    return MGPU_B200_E_INVALID;
+  if(op < MGPU_B200_PLUS || op > MGPU_B200_MIN) return MGPU_B200_E_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  char* box = (char*)mailbox_device;
+  unsigned long long* values =
+    (unsigned long long*)(box + mailbox_scratch_offset);
+  uint32_t* has = (uint32_t*)(values + lead_ctas);
+  uint32_t* ticket = has + lead_ctas;
+  chain_t chain = { (char* const*)peers_device, shard, num_shards,
+    shards_per_gpu, step, timeout_ns ? timeout_ns : default_mailbox_wait_ns };
+  switch(dtype) {
+    case MGPU_B200_F32: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
+      (const float*)input_device, starts_device, num_starts, count, op,
+      nullptr, values, has, ticket, chain, box); break;
+    case MGPU_B200_F64: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
+      (const double*)input_device, starts_device, num_starts, count, op,
+      nullptr, values, has, ticket, chain, box); break;
+    case MGPU_B200_I32: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
+      (const int*)input_device, starts_device, num_starts, count, op,
+      nullptr, values, has, ticket, chain, box); break;
+    case MGPU_B200_I64: shard_lead_k<<<lead_ctas, lead_threads, 0, s>>>(
+      (const long long*)input_device, starts_device, num_starts, count, op,
+      nullptr, values, has, ticket, chain, box); break;
+    default: return MGPU_B200_E_UNSUPPORTED;
+  }
+  return code_of(cudaGetLastError());
+}
+
+int mgpu_b200_shard_collect(int dtype, int op, void* mailbox_device,
+  const void* const* peers_device, int shard, int num_shards,
+  int shards_per_gpu, unsigned step, void* out_device, int num_starts,
+  const void* init_host, uint64_t timeout_ns, void* stream) {
+  if(!out_device || !init_host || num_starts < 1 ||
+    !chain_ok(mailbox_device, peers_device, shard, num_shards, shards_per_gpu,
+      step))
+    return MGPU_B200_E_INVALID;
+  if(op < MGPU_B200_PLUS || op > MGPU_B200_MIN) return MGPU_B200_E_UNSUPPORTED;
+  cudaStream_t s = (cudaStream_t)stream;
+  char* box = (char*)mailbox_device;
+  chain_t chain = { (char* const*)peers_device, shard, num_shards,
+    shards_per_gpu, step, timeout_ns ? timeout_ns : default_mailbox_wait_ns };
+  switch(dtype) {
+    case MGPU_B200_F32: { float i; memcpy(&i, init_host, 4);
+      shard_collect_k<<<1, 32, 0, s>>>(box, chain, op, (float*)out_device,
+        num_starts, i); break; }
+    case MGPU_B200_F64: { double i; memcpy(&i, init_host, 8);
+      shard_collect_k<<<1, 32, 0, s>>>(box, chain, op, (double*)out_device,
+        num_starts, i); break; }
+    case MGPU_B200_I32: { int i; memcpy(&i, init_host, 4);
+      shard_collect_k<<<1, 32, 0, s>>>(box, chain, op, (int*)out_device,
+        num_starts, i); break; }
+    case MGPU_B200_I64: { long long i; memcpy(&i, init_host, 8);
+      shard_collect_k<<<1, 32, 0, s>>>(box, chain, op, (long long*)out_device,
+        num_starts, i); break; }
     default: return MGPU_B200_E_UNSUPPORTED;
   }
   return code_of(cudaGetLastError());

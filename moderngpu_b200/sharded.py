@@ -16,6 +16,13 @@ stream on the current device); this layer is new. Data path per rank:
 With overlap=False the record is taken from the reduction's own first output
 instead (mgpu_b200_shard_pack) and the exchange follows the reduction.
 
+With a `Mailbox` the exchange needs no collective at all: step 1 becomes
+mgpu_b200_shard_post, which stores the record straight into the memory of
+the GPUs that hold earlier shards (peer-to-peer stores over NVLink into
+memory mapped with CUDA IPC), step 2 disappears, and step 4 becomes
+mgpu_b200_shard_collect, which waits -- in its own GPU's memory, for a
+bounded time -- for the records it needs.
+
 Shard-local start table: entry 0 is always 0 and stands for the segment
 carried in from the previous rank; the remaining entries are the local offsets
 of the segments that START inside the shard. `shard_table` derives it from a
@@ -94,6 +101,85 @@ def fold_plan(flags, rank):
     return take
 
 
+class Mailbox:
+    """This rank's mailbox and its mapping of every other rank's mailbox.
+
+    Collective over `group`: every rank constructs one at the same time (the
+    64-byte handles travel through the process group once, at set-up; no
+    collective runs in the data path afterwards). shards_per_gpu: how many
+    consecutive shards of the chain each rank holds. Use one Mailbox per
+    stream, call `close()` (collective) when done."""
+
+    def __init__(self, group=None, shards_per_gpu=1, device=None,
+                 timeout_ns=0):
+        lib = binding.load_library()
+        self.lib = lib
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.per_gpu = shards_per_gpu
+        self.num_shards = self.world * shards_per_gpu
+        self.timeout_ns = timeout_ns
+        self.step = 0
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = device
+        own = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(device):
+            binding._check(lib.mgpu_b200_mailbox_create(ctypes.byref(own),
+                                                        handle))
+        self.own = own.value
+        handles = [bytes(handle)]
+        if self.world > 1:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+        self.opened = []
+        pointers = []
+        with torch.cuda.device(device):
+            for k in range(self.world):
+                if k == self.rank:
+                    pointers.append(self.own)
+                    continue
+                peer = ctypes.c_void_p()
+                raw = (ctypes.c_ubyte * 64).from_buffer_copy(handles[k])
+                binding._check(lib.mgpu_b200_mailbox_open(raw,
+                                                          ctypes.byref(peer)))
+                self.opened.append(peer.value)
+                pointers.append(peer.value)
+        self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
+        torch.cuda.synchronize(device)
+        if self.world > 1:
+            dist.barrier(group=group)
+
+    def next_step(self):
+        self.step += 1
+        return self.step
+
+    def status(self):
+        """0, or the code of the first bounded wait that ran out (3: a record
+        did not arrive, 4: a ring slot was not released). Synchronises."""
+        out = ctypes.c_int(0)
+        with torch.cuda.device(self.device):
+            binding._check(self.lib.mgpu_b200_mailbox_status(
+                self.own, binding._stream(self.device), ctypes.byref(out)))
+        return out.value
+
+    def close(self):
+        if self.own is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)     # nobody still writes to anybody
+        with torch.cuda.device(self.device):
+            for peer in self.opened:
+                binding._check(self.lib.mgpu_b200_mailbox_close(peer))
+            if self.world > 1:
+                dist.barrier(group=self.group)  # every mapping is gone
+            binding._check(self.lib.mgpu_b200_mailbox_destroy(self.own))
+        self.own, self.opened = None, []
+
+
 _lead_scratch = {}
 
 
@@ -110,7 +196,7 @@ def lead_scratch(dev):
 
 
 def sharded_segreduce(values, table, op="plus", init=0, group=None,
-                      records=None, overlap=True):
+                      records=None, overlap=True, mailbox=None):
     """Reduce this rank's shard and fold boundary partials across ranks.
 
     values: this rank's items (CUDA tensor); table: its shard-local start
@@ -121,6 +207,9 @@ def sharded_segreduce(values, table, op="plus", init=0, group=None,
     if not values.is_cuda:
         raise binding.LibraryMissing(
             "sharded_segreduce runs on CUDA tensors only (no CPU fallback)")
+    if mailbox is not None:
+        return sharded_segreduce_multi([(values, table)], op=op, init=init,
+                                       mailbox=mailbox)[0]
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     return _sharded_cuda(values, table, op, init, group, rank, world, records,
@@ -166,8 +255,42 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records,
     return out
 
 
+def _sharded_mailbox(shards, op, init, outs, workspace, mailbox):
+    """Post every shard's record, reduce every shard, collect."""
+    lib = mailbox.lib
+    k = len(shards)
+    if k != mailbox.per_gpu:
+        raise ValueError("the mailbox was set up for %d shards per GPU" %
+                         mailbox.per_gpu)
+    dev = shards[0][0].device
+    dtype = binding._DTYPES[shards[0][0].dtype]
+    stream = binding._stream(dev)
+    step = mailbox.next_step()
+    first = mailbox.rank * k
+    init_c = binding._CTYPES[shards[0][0].dtype](init)
+    results = []
+    with torch.cuda.device(dev):
+        for j, (values, table) in enumerate(shards):
+            binding._check(lib.mgpu_b200_shard_post(
+                dtype, binding._OPS[op], values.data_ptr(), values.numel(),
+                table.data_ptr(), table.numel(), mailbox.own,
+                mailbox.peers.data_ptr(), first + j, mailbox.num_shards, k,
+                step, mailbox.timeout_ns, stream))
+        for j, (values, table) in enumerate(shards):
+            results.append(binding.segreduce(
+                values, table, op=op, init=init,
+                out=None if outs is None else outs[j], workspace=workspace))
+        for j, (values, table) in enumerate(shards):
+            binding._check(lib.mgpu_b200_shard_collect(
+                dtype, binding._OPS[op], mailbox.own,
+                mailbox.peers.data_ptr(), first + j, mailbox.num_shards, k,
+                step, results[j].data_ptr(), table.numel(),
+                ctypes.byref(init_c), mailbox.timeout_ns, stream))
+    return results
+
+
 def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
-                            workspace=None, overlap=True):
+                            workspace=None, overlap=True, mailbox=None):
     """Several consecutive shards per rank (CUDA tensors only).
 
     shards: list of (values, table) pairs held by this rank, in array order;
@@ -176,7 +299,10 @@ def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
     array exceeds what a single call can index (count + segments < 2^31), for
     instance the whole 2^32-item array on one GPU as 8 shards. One all-gather
     of k records per rank; the fold treats the world*k shards as one chain.
-    Returns the list of per-shard outputs."""
+    Returns the list of per-shard outputs. With `mailbox` the records travel
+    by peer-to-peer stores and no collective runs."""
+    if mailbox is not None:
+        return _sharded_mailbox(shards, op, init, outs, workspace, mailbox)
     lib = binding.load_library()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0

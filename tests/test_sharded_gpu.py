@@ -52,9 +52,18 @@ def worker(rank, world, port, kind, dtype_name, op, overlap, queue):
         dtype = np.dtype(dtype_name).type
         values, seg = make_problem(kind, dtype)
         begin, end, first, table = sharded.shard_table(seg, values.size, rank, world)
-        out = sharded.sharded_segreduce(
-            torch.from_numpy(values[begin:end].copy()).cuda(),
-            torch.from_numpy(table).cuda(), op=op, init=-7, overlap=overlap)
+        v = torch.from_numpy(values[begin:end].copy()).cuda()
+        t = torch.from_numpy(table).cuda()
+        if overlap == "mailbox":
+            # Peer-to-peer records, no collective in the data path; 70 steps
+            # so that the 64-slot ring wraps and the acks are exercised.
+            box = sharded.Mailbox()
+            for _ in range(70):
+                out = sharded.sharded_segreduce(v, t, op=op, init=-7, mailbox=box)
+            assert box.status() == 0
+            box.close()
+        else:
+            out = sharded.sharded_segreduce(v, t, op=op, init=-7, overlap=overlap)
         torch.cuda.synchronize()
         pieces = [None] * world
         dist.all_gather_object(pieces, (first, out.cpu().numpy()[1:].tolist()))
@@ -69,6 +78,9 @@ def worker(rank, world, port, kind, dtype_name, op, overlap, queue):
     ("few_long", "int32", "plus", True), ("one", "float64", "min", True),
     ("lognormal", "float64", "plus", True), ("lognormal", "int64", "plus", False),
     ("few_long", "int32", "plus", False),
+    ("lognormal", "float64", "max", "mailbox"), ("lognormal", "int64", "plus", "mailbox"),
+    ("few_long", "int32", "plus", "mailbox"), ("one", "float64", "min", "mailbox"),
+    ("lognormal", "float64", "plus", "mailbox"),
 ])
 def test_sharded_matches_oracle(oracle, kind, dtype, op, overlap):
     world = min(torch.cuda.device_count(), 4)
@@ -98,7 +110,7 @@ def test_sharded_matches_oracle(oracle, kind, dtype, op, overlap):
         assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("overlap", [True, False])
+@pytest.mark.parametrize("overlap", [True, False, "mailbox"])
 @pytest.mark.parametrize("kind,dtype,op", [
     ("lognormal", "float64", "max"), ("few_long", "int64", "plus"),
     ("one", "int32", "plus"),
@@ -115,8 +127,16 @@ def test_several_shards_on_one_gpu(mgpu, oracle, kind, dtype, op, overlap):
         shards.append((torch.from_numpy(values[begin:end].copy()).cuda(),
                        torch.from_numpy(table).cuda()))
         firsts.append(first)
-    outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7,
-                                           overlap=overlap)
+    if overlap == "mailbox":
+        box = sharded.Mailbox(shards_per_gpu=pieces)
+        for _ in range(3):
+            outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7,
+                                                   mailbox=box)
+        assert box.status() == 0
+        box.close()
+    else:
+        outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7,
+                                               overlap=overlap)
     got = np.zeros(seg.size, dtype=np.float64)
     for first, out in zip(firsts, outs):
         vals = out.cpu().numpy()[1:]
@@ -160,3 +180,51 @@ def test_lead_record_equals_pack_record(mgpu, dtype, op, lead):
     assert got[0, 1] == got[1, 1] == got[2, 1]            # flags
     if lead > 0:
         assert got[0, 0] == got[1, 0] == got[2, 0]        # the partial's bits
+
+
+def _post(lib, box, v, t, shard, num_shards, step, timeout_ns):
+    from moderngpu_b200 import binding
+    binding._check(lib.mgpu_b200_shard_post(
+        binding._DTYPES[v.dtype], binding._OPS["plus"], v.data_ptr(), v.numel(),
+        t.data_ptr(), t.numel(), box.own, box.peers.data_ptr(), shard,
+        num_shards, num_shards, step, timeout_ns, binding._stream(v.device)))
+
+
+def test_mailbox_waits_are_bounded(mgpu):
+    """A record that nobody posts and a ring slot that nobody releases: the
+    waiting kernel gives up after its time limit, reports it through the
+    mailbox's status word, leaves the output alone, and the context stays
+    usable. One GPU, two shards of a chain, both held here."""
+    import ctypes
+    from moderngpu_b200 import binding
+    lib = binding.load_library()
+    v = torch.arange(1000, dtype=torch.int32, device="cuda")
+    t = torch.tensor([0, 10, 500], dtype=torch.int32, device="cuda")
+    out = mgpu.segreduce(v, t, op="plus", init=0)
+    before = out.clone()
+    limit = 3_000_000                       # 3 ms
+
+    # (a) shard 0 collects, shard 1 never posted.
+    box = sharded.Mailbox(shards_per_gpu=2)
+    _post(lib, box, v, t, 0, 2, 1, limit)
+    init = ctypes.c_int(0)
+    binding._check(lib.mgpu_b200_shard_collect(
+        binding._DTYPES[v.dtype], binding._OPS["plus"], box.own,
+        box.peers.data_ptr(), 0, 2, 2, 1, out.data_ptr(), t.numel(),
+        ctypes.byref(init), limit, binding._stream(v.device)))
+    assert box.status() == 3
+    assert torch.equal(out, before)
+    box.close()
+
+    # (b) 65 posts and no collect: the 65th finds its ring slot still taken.
+    box = sharded.Mailbox(shards_per_gpu=1)
+    for step in range(1, 65):
+        _post(lib, box, v, t, 0, 1, step, limit)
+    assert box.status() == 0
+    _post(lib, box, v, t, 0, 1, 65, limit)
+    assert box.status() == 4
+    box.close()
+
+    # The context still works.
+    again = mgpu.segreduce(v, t, op="plus", init=0)
+    assert torch.equal(again, before)
