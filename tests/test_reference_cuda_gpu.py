@@ -186,3 +186,16 @@ def test_template_program_on_the_reference_itself():
     failed = [l for l in run.stdout.splitlines() if l.rstrip().endswith("FAIL")]
     tolerated = [l for l in failed if "24-byte type" in l]
     assert failed == tolerated, run.stdout
+
+
+def test_nearest_pipeline_on_the_reference_itself():
+    """tests/cpp/test_nearest_pipeline.cu compiled against the REFERENCE's
+    headers: its merge operator breaks ties by index, so the reference's
+    operand order in the fix-up does not show and every check must pass on
+    the reference exactly as it does on this library."""
+    exe = os.path.join(REF_DIR, "nearest_pipeline_on_reference")
+    if not os.path.exists(exe):
+        pytest.skip("reference-built pipeline program not present")
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert "FAIL" not in run.stdout, run.stdout
+    assert "ALL PASSED" in run.stdout, run.stdout + run.stderr

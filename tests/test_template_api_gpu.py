@@ -13,11 +13,32 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 EXE = os.path.join(ROOT, "tests", "cpp", "build", "test_template_api")
 
 
+PIPELINE = os.path.join(ROOT, "tests", "cpp", "build", "test_nearest_pipeline")
+
+
+def run_program(exe):
+    if not os.path.exists(exe):
+        pytest.fail("%s is not built: run "
+                    "python -c 'import __graft_entry__ as g; g.build()'"
+                    % os.path.relpath(exe, ROOT))
+    return subprocess.run([exe], capture_output=True, text=True, timeout=300)
+
+
+def test_nearest_pipeline():
+    """tests/cpp/test_nearest_pipeline.cu: scan -> interval_expand ->
+    transform_lbs -> scan in place -> lbs_segreduce with a 24-byte type and a
+    user-written merge operator, the call chain of the reference's
+    demo/cities.cu:143-236 on seeded synthetic points, bit for bit against a
+    brute-force host loop."""
+    run = run_program(PIPELINE)
+    print(run.stdout)
+    assert "FAIL" not in run.stdout, run.stdout
+    assert "ALL PASSED" in run.stdout, run.stdout + run.stderr
+    assert run.returncode == 0
+
+
 def test_template_entry_points():
-    if not os.path.exists(EXE):
-        pytest.fail("tests/cpp/build/test_template_api is not built: run "
-                    "python -c 'import __graft_entry__ as g; g.build()'")
-    run = subprocess.run([EXE], capture_output=True, text=True, timeout=300)
+    run = run_program(EXE)
     print(run.stdout)
     assert "FAIL" not in run.stdout, run.stdout
     assert "ALL PASSED" in run.stdout, run.stdout + run.stderr
