@@ -91,6 +91,28 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src,
        "r"(smem_addr(bar)) : "memory");
 }
 
+// Bulk copy shared memory of the issuing CTA -> global. The issuing thread
+// groups its copies (commit) and waits either until their source has been
+// read (the shared memory may be reused) or until they are complete. These
+// waits concern the thread's own copies only and always end.
+__device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src,
+  uint32_t bytes) {
+  asm volatile(
+    "cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+    :: "l"(gmem_dst), "r"(smem_addr(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template<int pending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(pending) : "memory");
+}
+template<int pending>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" :: "n"(pending) : "memory");
+}
+
 // Programmatic dependent launch: a kernel launched with the programmatic
 // stream-serialization attribute may start while its predecessor in the
 // stream is still running; it must call grid_dependency_wait() before it

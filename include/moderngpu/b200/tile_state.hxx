@@ -192,6 +192,12 @@ MGPU_DEVICE type_t shfl_up_any(const type_t& x, int delta) {
   return y;
 }
 
+template<typename type_t>
+MGPU_DEVICE type_t shfl_down_any(const type_t& x, int delta) {
+  int lane = (int)(threadIdx.x & 31);
+  return shfl_any(x, lane + delta < 32 ? lane + delta : lane);
+}
+
 // Executed by one full warp of tile `tile` (> 0): fold what tiles
 // tile-1, tile-2, ... contribute to the segment that is open at this tile's
 // left edge. Returns true and sets `carry` when there is a contribution.
@@ -275,6 +281,96 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
     }
     if(stop < 32) break;
     base -= 32;
+  }
+  if(have) carry = acc;
+  return have;
+}
+
+// Look-back for a chain in which EVERY tile depends on all earlier ones (a
+// prefix scan: no tile_closed words, few tile_inclusive words near the
+// front). The inclusive front advances by at most one window per round trip
+// to the L2, so the window is `rows` x 32 tiles wide: lane l reads tiles
+// base - l - 32 r for r < rows, all loads in flight together, and the rows
+// are folded with a shuffle tree. Executed by one full warp of tile `tile`
+// (> 0). Returns true and sets `carry` (the fold of all earlier tiles); on
+// expiry of `timeout_ns` sets *status and returns false.
+template<int rows, typename type_t, typename op_t>
+MGPU_DEVICE bool lookback_wide(const tile_state_t<type_t>& state, int tile,
+  op_t op, type_t& carry, uint64_t timeout_ns, uint32_t* status) {
+  const unsigned full = 0xffffffffu;
+  const int lane = (int)(threadIdx.x & 31);
+  bool have = false;
+  type_t acc = carry;
+  int base = tile - 1;
+  uint64_t start = 0;
+  uint32_t spin = 0;
+
+  while(true) {
+    uint32_t code[rows];
+    type_t value[rows];
+    #pragma unroll
+    for(int r = 0; r < rows; ++r) {
+      int idx = base - lane - 32 * r;
+      code[r] = tile_inclusive;         // before tile 0: the chain ends here
+      value[r] = carry;
+      if(idx >= 0) code[r] = state.peek(idx, value[r]);
+    }
+    // Rows are used front to back until one holds a final word or a gap.
+    bool done = false, gap = false;
+    #pragma unroll
+    for(int r = 0; r < rows; ++r) {
+      if(done || gap) continue;
+      bool before_zero = base - lane - 32 * r < 0;
+      unsigned final_mask = __ballot_sync(full, code[r] >= tile_inclusive);
+      unsigned empty_mask = __ballot_sync(full, tile_empty == code[r]);
+      int stop = final_mask ? __ffs(final_mask) - 1 : 32;
+      unsigned needed = stop >= 31 ? full : ((2u << stop) - 1);
+      if(empty_mask & needed) {
+        // Use the published words in front of the first gap, then poll again
+        // from the gap on.
+        int first_gap = __ffs(empty_mask & needed) - 1;
+        stop = first_gap - 1;            // last usable lane (may be -1)
+        gap = true;
+        needed = first_gap ? ((1u << first_gap) - 1) : 0u;
+      }
+      // Fold lanes [0, min(stop, 31)], the earliest tile (highest lane) first.
+      int last = stop < 31 ? stop : 31;
+      bool mine = lane <= last && !(before_zero);
+      type_t x = value[r];
+      #pragma unroll
+      for(int delta = 1; delta < 32; delta *= 2) {
+        type_t up = shfl_down_any(x, delta);
+        bool up_have = __shfl_down_sync(full, mine, delta) && lane + delta < 32;
+        if(up_have) { x = mine ? op(up, x) : up; mine = true; }
+      }
+      x = shfl_any(x, 0);
+      bool row_have = __shfl_sync(full, mine, 0);
+      if(row_have) {
+        acc = have ? op(x, acc) : x;
+        have = true;
+      }
+      if(gap) base -= 32 * r + (stop + 1);
+      else if(stop < 32) done = true;
+    }
+    if(done) break;
+    if(!gap) { base -= 32 * rows; continue; }
+    // Tile `base` had not published anything yet: poll that one word (every
+    // lane the same address) until it has, then read the window again.
+    while(true) {
+      type_t ignored = carry;
+      uint32_t c = state.peek(base, ignored);
+      if(tile_empty != __shfl_sync(full, c, 0)) break;
+      if(spin > 8) __nanosleep(32);
+      if(15 == (spin & 15)) {
+        uint64_t now = __shfl_sync(full, ptx::global_timer_ns(), 0);
+        if(!start) start = now;
+        else if(now - start > timeout_ns) {
+          if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);
+          return false;
+        }
+      }
+      ++spin;
+    }
   }
   if(have) carry = acc;
   return have;

@@ -288,25 +288,25 @@ __global__ void lookback_probe_k(void* state_words, int tile,
 template<typename type_t>
 int scan_typed(int inclusive, const void* input, int count, void* output,
   void* total, void* workspace, cudaStream_t stream) {
-  typedef typename detail::scan_default_tuning<type_t>::type tuning_t;
+  typedef detail::scan_route_t<empty_t, type_t, const type_t*, type_t*> route_t;
   try {
     if(total) {
       if(inclusive)
-        detail::scan_enqueue<tuning_t, scan_type_inc, type_t>(
+        detail::scan_dispatch<route_t, scan_type_inc, type_t>(
           (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
           (type_t*)total, workspace, stream, g_timeout_ns);
       else
-        detail::scan_enqueue<tuning_t, scan_type_exc, type_t>(
+        detail::scan_dispatch<route_t, scan_type_exc, type_t>(
           (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
           (type_t*)total, workspace, stream, g_timeout_ns);
     } else {
       discard_iterator_t<type_t> nowhere;
       if(inclusive)
-        detail::scan_enqueue<tuning_t, scan_type_inc, type_t>(
+        detail::scan_dispatch<route_t, scan_type_inc, type_t>(
           (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
           nowhere, workspace, stream, g_timeout_ns);
       else
-        detail::scan_enqueue<tuning_t, scan_type_exc, type_t>(
+        detail::scan_dispatch<route_t, scan_type_exc, type_t>(
           (const type_t*)input, count, (type_t*)output, plus_t<type_t>(),
           nowhere, workspace, stream, g_timeout_ns);
     }
