@@ -495,6 +495,11 @@ def run_other_config(args, rank, world, local_rank):
         steps["spmv fp32 nnz=%d" % m.numel()] = (
             lambda: mgpu.spmv(m, c, x, r, out=y), m.numel(),
             workloads.spmv_bytes(m.numel(), r.numel(), x.numel(), 4))
+        # The same with the x vector pinned in the L2 (mgpu_b200_l2_pin); the
+        # pin is taken before this case's warm-up and dropped after the run.
+        steps["spmv fp32, x pinned in L2"] = (
+            lambda: mgpu.spmv(m, c, x, r, out=y), m.numel(),
+            workloads.spmv_bytes(m.numel(), r.numel(), x.numel(), 4))
     elif cfg == "c4":
         count = 1 << 28
         s = workloads.config4(seed=3, device=device)
@@ -533,6 +538,8 @@ def run_other_config(args, rank, world, local_rank):
     peak, peak_kind = measured_peak()
     results = []
     for name, (fn, units, nbytes) in steps.items():
+        if "pinned" in name:
+            mgpu.l2_pin(x)
         for _ in range(max(args.warmup, 3)):
             fn()
         if world > 1:
@@ -550,6 +557,8 @@ def run_other_config(args, rank, world, local_rank):
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
+        if "pinned" in name:
+            mgpu.l2_unpin()
         gbs = nbytes / (ms * 1e-3) / 1e9
         results.append({"case": name, "ms_per_step": ms,
                         "gitems_per_s": world * units / (ms * 1e-3) / 1e9,

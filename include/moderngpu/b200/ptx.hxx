@@ -169,6 +169,25 @@ __device__ __forceinline__ type_t ld_nc_hint(const type_t* p, uint64_t policy) {
   return v;
 }
 
+// The same without a line in the L1: for gathers that never hit there.
+template<typename type_t>
+__device__ __forceinline__ type_t ld_no_l1_hint(const type_t* p, uint64_t policy) {
+  static_assert(sizeof(type_t) == 4 || sizeof(type_t) == 8, "4 or 8 bytes");
+  type_t v;
+  if constexpr (sizeof(type_t) == 4) {
+    uint32_t bits;
+    asm volatile("ld.global.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;"
+      : "=r"(bits) : "l"(p), "l"(policy));
+    memcpy(&v, &bits, 4);
+  } else {
+    uint64_t bits;
+    asm volatile("ld.global.L1::no_allocate.L2::cache_hint.b64 %0, [%1], %2;"
+      : "=l"(bits) : "l"(p), "l"(policy));
+    memcpy(&v, &bits, 8);
+  }
+  return v;
+}
+
 ////////////////////////////////////////////////////////////////////////////////
 // Named barrier over `count` threads (a multiple of 32) of the CTA.
 

@@ -190,6 +190,21 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
   const void* init_host, void* reserved);
 
 /*
+ * Optional L2 residency for an array that later calls on `stream` gather from
+ * at random -- the vector of mgpu_b200_spmv. No counterpart in the reference.
+ * mgpu_b200_l2_pin sets aside min(bytes, the device's maximum) of this
+ * context's L2 for persisting lines and attaches an access-policy window over
+ * the array to the stream; kernels launched on the stream afterwards keep the
+ * array's lines in preference to everything they stream through.
+ * mgpu_b200_l2_unpin removes the window, releases the persisting lines and
+ * returns the set-aside to zero. Both are settings of the calling process's
+ * CUDA context only; nothing outlasts the process. A caller that manages the
+ * set-aside itself should not use these.
+ */
+int mgpu_b200_l2_pin(const void* array_device, size_t bytes, void* stream);
+int mgpu_b200_l2_unpin(void* stream);
+
+/*
  * mgpu::scan with plus (reference: src/moderngpu/kernel_scan.hxx:159-175):
  * exclusive (inclusive == 0: output[i] = sum of input[0 .. i), output[0] = 0)
  * or inclusive prefix sums of `count` elements of `dtype`; the usual way to

@@ -11,6 +11,8 @@ from .binding import (  # noqa: F401
     LibraryMissing,
     MgpuError,
     interval_expand,
+    l2_pin,
+    l2_unpin,
     lib_path,
     load_balance_partitions,
     load_balance_search,
@@ -26,7 +28,7 @@ from .binding import (  # noqa: F401
 )
 
 __all__ = [
-    "LibraryMissing", "MgpuError", "interval_expand", "lib_path",
+    "LibraryMissing", "MgpuError", "interval_expand", "l2_pin", "l2_unpin", "lib_path",
     "load_balance_partitions", "load_balance_search", "load_library", "scan",
     "segreduce", "segreduce_host", "segreduce_profile",
     "segreduce_static", "spmv", "transform_lbs", "workspace_status",

@@ -124,6 +124,10 @@ def _declare_optional(lib):
     lib.mgpu_b200_shard_lead.argtypes = [
         c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
         c_void_p]
+    lib.mgpu_b200_l2_pin.restype = c_int
+    lib.mgpu_b200_l2_pin.argtypes = [c_void_p, c_size_t, c_void_p]
+    lib.mgpu_b200_l2_unpin.restype = c_int
+    lib.mgpu_b200_l2_unpin.argtypes = [c_void_p]
     lib.mgpu_b200_mailbox_bytes.restype = c_size_t
     lib.mgpu_b200_mailbox_bytes.argtypes = []
     lib.mgpu_b200_mailbox_create.restype = c_int
@@ -220,6 +224,25 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
             num_segments, out.data_ptr(), ctypes.byref(init_c),
             workspace.data_ptr(), workspace.numel(), _stream(input.device)))
     return out
+
+
+def l2_pin(array):
+    """Keep `array` (the vector later spmv calls on the current stream gather
+    from) resident in the L2: mgpu_b200_l2_pin. Undo with l2_unpin()."""
+    lib = load_library()
+    _require_cuda(array, "array")
+    with torch.cuda.device(array.device):
+        _check(lib.mgpu_b200_l2_pin(array.data_ptr(),
+                                    array.numel() * array.element_size(),
+                                    _stream(array.device)))
+
+
+def l2_unpin(device=None):
+    lib = load_library()
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    with torch.cuda.device(device):
+        _check(lib.mgpu_b200_l2_unpin(_stream(device)))
 
 
 def scan(input, inclusive=False, out=None, total=None, workspace=None):

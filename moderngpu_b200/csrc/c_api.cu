@@ -587,6 +587,47 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
     segments_host, num_segments, (char*)output_host, init_host);
 }
 
+int mgpu_b200_l2_pin(const void* array_device, size_t bytes, void* stream) {
+  if(!array_device || !bytes) return MGPU_B200_E_INVALID;
+  int device = 0, max_persisting = 0, max_window = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if(cudaSuccess == e) e = cudaDeviceGetAttribute(&max_persisting,
+    cudaDevAttrMaxPersistingL2CacheSize, device);
+  if(cudaSuccess == e) e = cudaDeviceGetAttribute(&max_window,
+    cudaDevAttrMaxAccessPolicyWindowSize, device);
+  if(cudaSuccess != e) return cuda_code(e);
+  if(max_persisting <= 0 || max_window <= 0) return MGPU_B200_E_UNSUPPORTED;
+  size_t set_aside = bytes < (size_t)max_persisting ? bytes :
+    (size_t)max_persisting;
+  e = cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, set_aside);
+  if(cudaSuccess != e) return cuda_code(e);
+  cudaStreamAttrValue value = { };
+  value.accessPolicyWindow.base_ptr = const_cast<void*>(array_device);
+  value.accessPolicyWindow.num_bytes = bytes < (size_t)max_window ? bytes :
+    (size_t)max_window;
+  // Only as large a share of the window as the set-aside can hold is marked
+  // persisting; the rest streams, so the persisting lines do not evict each
+  // other.
+  value.accessPolicyWindow.hitRatio =
+    (float)((double)set_aside / (double)value.accessPolicyWindow.num_bytes);
+  if(value.accessPolicyWindow.hitRatio > 1.0f)
+    value.accessPolicyWindow.hitRatio = 1.0f;
+  value.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+  value.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+  return cuda_code(cudaStreamSetAttribute((cudaStream_t)stream,
+    cudaStreamAttributeAccessPolicyWindow, &value));
+}
+
+int mgpu_b200_l2_unpin(void* stream) {
+  cudaStreamAttrValue value = { };
+  value.accessPolicyWindow.num_bytes = 0;
+  cudaError_t e = cudaStreamSetAttribute((cudaStream_t)stream,
+    cudaStreamAttributeAccessPolicyWindow, &value);
+  if(cudaSuccess == e) e = cudaCtxResetPersistingL2Cache();
+  if(cudaSuccess == e) e = cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, 0);
+  return cuda_code(e);
+}
+
 size_t mgpu_b200_scan_workspace_bytes(int dtype, int count) {
   if(count < 0) return 0;
   switch(dtype) {

@@ -46,3 +46,23 @@ def test_config3_full_size(mgpu, oracle):
                              r.cpu().numpy())
     err = np.abs(y.cpu().numpy().astype(np.float64) - want)
     assert np.all(err <= 1e-5 * np.maximum(np.abs(want), mags))
+
+
+def test_l2_pin_leaves_results_unchanged(mgpu):
+    """mgpu_b200_l2_pin / _unpin only change where the vector's lines live:
+    the product is bit-identical with and without the pin, and a second
+    pin/unpin cycle works."""
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rows, per_row = 200_000, 9
+    nnz = rows * per_row
+    m = torch.rand(nnz, device="cuda", generator=g) * 2 - 1
+    c = torch.randint(0, rows, (nnz,), device="cuda", generator=g, dtype=torch.int32)
+    x = torch.rand(rows, device="cuda", generator=g) * 2 - 1
+    r = torch.arange(0, nnz, per_row, device="cuda", dtype=torch.int32)
+    plain = mgpu.spmv(m, c, x, r).clone()
+    for _ in range(2):
+        mgpu.l2_pin(x)
+        pinned = mgpu.spmv(m, c, x, r).clone()
+        mgpu.l2_unpin()
+        assert torch.equal(plain, pinned)
+    assert torch.equal(plain, mgpu.spmv(m, c, x, r))
