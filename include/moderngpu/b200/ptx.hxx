@@ -196,6 +196,23 @@ __device__ __forceinline__ void named_sync() {
   asm volatile("bar.sync %0, %1;" :: "n"(id), "n"(count) : "memory");
 }
 
+// The same barrier with a vote: true for all `count` threads iff `mine` is
+// true for all of them. Lets a subset of a CTA agree to leave a loop together
+// after a bounded wait has run out for some of its threads.
+template<int id, int count>
+__device__ __forceinline__ bool named_all(bool mine) {
+  uint32_t out;
+  asm volatile(
+    "{\n"
+    "  .reg .pred p, q;\n"
+    "  setp.ne.u32 q, %1, 0;\n"
+    "  bar.red.and.pred p, %2, %3, q;\n"
+    "  selp.u32 %0, 1, 0, p;\n"
+    "}\n"
+    : "=r"(out) : "r"((uint32_t)mine), "n"(id), "n"(count) : "memory");
+  return out != 0;
+}
+
 ////////////////////////////////////////////////////////////////////////////////
 // Device-scope loads and stores for flags shared between CTAs.
 

@@ -232,21 +232,6 @@ struct scan_stream_default_tuning<type_t, 8> {
   typedef scan_stream_tuning_t<512, 18> type;
 };
 
-// True for all threads of the named barrier iff `mine` is true for all.
-template<int id, int count>
-__device__ __forceinline__ bool named_all(bool mine) {
-  uint32_t out;
-  asm volatile(
-    "{\n"
-    "  .reg .pred p, q;\n"
-    "  setp.ne.u32 q, %1, 0;\n"
-    "  bar.red.and.pred p, %2, %3, q;\n"
-    "  selp.u32 %0, 1, 0, p;\n"
-    "}\n"
-    : "=r"(out) : "r"((uint32_t)mine), "n"(id), "n"(count) : "memory");
-  return out != 0;
-}
-
 template<typename tuning_t, scan_type_t scan_type, typename type_t,
   typename op_t, typename reduction_it>
 __global__ void __launch_bounds__(tuning_t::nt + 64, tuning_t::occ)
@@ -437,7 +422,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
       type_t before = shfl_up_any(incl, 1);
       bool before_have = __shfl_up_sync(all_lanes, incl_have, 1) && lane > 0;
       if(31 == lane) warp_total[k & 1][warp] = incl;
-      arrived = named_all<1, nt>(arrived);
+      arrived = ptx::named_all<1, nt>(arrived);
 
       const int warps_used = (n + 32 * vt - 1) / (32 * vt);
       type_t aggregate = warp_total[k & 1][0];
@@ -454,7 +439,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
         ptx::mbar_arrive(&agg_ready[s]);
       }
     } else {
-      arrived = named_all<1, nt>(arrived);
+      arrived = ptx::named_all<1, nt>(arrived);
       if(0 == tid) ptx::mbar_arrive(&agg_ready[s]);     // lets the carry warp leave
     }
     if(!arrived) {
