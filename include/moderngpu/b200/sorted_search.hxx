@@ -1,0 +1,170 @@
+// Vectorised sorted search and the relational inner join built on it, for
+// sm_100a.
+//
+// Interface parity (reference): sorted_search
+// src/moderngpu/kernel_sortedsearch.hxx:7-62 -- for every needle (sorted) the
+// lower or upper bound of its position in the haystack (sorted);
+// merge_path_partitions src/moderngpu/search.hxx:12-27; inner_join
+// src/moderngpu/kernel_join.hxx:9-48 -- all pairs (i, j) with
+// a[i] equivalent to b[j], as int2, ordered by i then j.
+//
+// These are callers of the load-balancing search: inner_join turns the
+// per-needle match counts into segment starts with a scan and lets
+// transform_lbs write one pair per output slot.
+//
+// The reference merges needles and haystack serially per thread over shared
+// memory. Here a tile (cut by the same merge-path partition, so that tiles
+// carry equal work whatever the key distribution) stages only its haystack
+// range in shared memory, and every needle of the tile does a binary search
+// over that range -- by construction of the partition its bound lies inside
+// it. Needles are read and indices written in striped order (coalesced).
+#pragma once
+#include "partition.hxx"
+#include "scan.hxx"
+#include "load_balance.hxx"
+
+#ifdef __CUDACC__
+
+BEGIN_MGPU_NAMESPACE
+
+template<int nt_, int vt_>
+struct search_tuning_t {
+  enum { nt = nt_, vt = vt_, nv = nt_ * vt_ };
+};
+
+namespace detail {
+
+typedef search_tuning_t<256, 8> search_default_tuning;
+
+template<typename launch_arg_t>
+struct pick_search_tuning { typedef search_default_tuning type; };
+template<int nt, int vt>
+struct pick_search_tuning<search_tuning_t<nt, vt> > {
+  typedef search_tuning_t<nt, vt> type;
+};
+
+// partitions[k] = number of `a` keys among the first min(k * spacing, total)
+// elements of merge(a, b).
+template<bounds_t bounds, typename a_it, typename b_it, typename comp_t>
+__global__ void merge_path_partitions_k(a_it a, int a_count, b_it b,
+  int b_count, int spacing, int num_partitions, comp_t comp, int* partitions) {
+  int k = (int)(blockIdx.x * blockDim.x + threadIdx.x);
+  if(k >= num_partitions) return;
+  long long diag = (long long)k * spacing;
+  long long total = (long long)a_count + b_count;
+  if(diag > total) diag = total;
+  partitions[k] = merge_path<bounds>(a, a_count, b, b_count, (int)diag, comp);
+}
+
+template<bounds_t bounds, typename tuning_t, typename type_t,
+  typename needles_it, typename haystack_it, typename indices_it,
+  typename comp_t>
+__global__ void __launch_bounds__(tuning_t::nt)
+sorted_search_k(needles_it needles, int num_needles, haystack_it haystack,
+  int num_haystack, indices_it indices, comp_t comp, const int* partitions) {
+  enum { nt = tuning_t::nt, nv = tuning_t::nv };
+  __shared__ type_t keys[nv];
+
+  const int tid = (int)threadIdx.x;
+  const int tile = (int)blockIdx.x;
+  const long long total = (long long)num_needles + num_haystack;
+  const long long d0 = (long long)tile * nv;
+  const long long d1 = d0 + nv < total ? d0 + nv : total;
+  const int a0 = partitions[tile], a1 = partitions[tile + 1];
+  const int b0 = (int)(d0 - a0), b1 = (int)(d1 - a1);
+  const int nb = b1 - b0;
+
+  for(int i = tid; i < nb; i += nt) keys[i] = haystack[b0 + i];
+  __syncthreads();
+
+  for(int i = a0 + tid; i < a1; i += nt) {
+    type_t key = needles[i];
+    int lo = 0, hi = nb;
+    while(lo < hi) {
+      int mid = (lo + hi) >> 1;
+      // lower: first position whose key is not less than the needle;
+      // upper: first position whose key is greater than the needle.
+      bool right = (bounds_upper == bounds) ? !comp(key, keys[mid]) :
+        comp(keys[mid], key);
+      if(right) lo = mid + 1;
+      else hi = mid;
+    }
+    indices[i] = b0 + lo;
+  }
+}
+
+} // namespace detail
+
+// The merge-path partition table of two sorted sequences, one entry per
+// `spacing` merged elements plus the closing one.
+template<bounds_t bounds, typename a_keys_it, typename b_keys_it,
+  typename comp_t>
+mem_t<int> merge_path_partitions(a_keys_it a, int64_t a_count, b_keys_it b,
+  int64_t b_count, int64_t spacing, comp_t comp, context_t& context) {
+  int num_partitions = (int)div_up(a_count + b_count, spacing) + 1;
+  mem_t<int> partitions(num_partitions, context);
+  detail::merge_path_partitions_k<bounds><<<div_up(num_partitions, 128), 128,
+    0, context.stream()>>>(a, (int)a_count, b, (int)b_count, (int)spacing,
+    num_partitions, comp, partitions.data());
+  return partitions;
+}
+
+template<bounds_t bounds, typename launch_arg_t = empty_t,
+  typename needles_it, typename haystack_it, typename indices_it,
+  typename comp_it>
+void sorted_search(needles_it needles, int num_needles, haystack_it haystack,
+  int num_haystack, indices_it indices, comp_it comp, context_t& context) {
+  typedef typename detail::pick_search_tuning<launch_arg_t>::type tuning_t;
+  typedef typename std::iterator_traits<needles_it>::value_type type_t;
+  if(num_needles < 0 || num_haystack < 0 ||
+    (int64_t)num_needles + num_haystack > (int64_t)0x7fffffff - 65536)
+    throw cuda_exception_t(cudaErrorInvalidValue);
+  if(!num_needles) return;
+  int num_tiles = (int)div_up((int64_t)num_needles + num_haystack,
+    (int64_t)tuning_t::nv);
+  mem_t<int> partitions = merge_path_partitions<bounds>(needles, num_needles,
+    haystack, num_haystack, (int64_t)tuning_t::nv, comp, context);
+  detail::sorted_search_k<bounds, tuning_t, type_t><<<num_tiles,
+    (int)tuning_t::nt, 0, context.stream()>>>(needles, num_needles, haystack,
+    num_haystack, indices, comp, partitions.data());
+}
+
+// All pairs (a_index, b_index) whose keys are equivalent under `comp`; both
+// inputs sorted by `comp`. The size of the result is known only after the
+// match counts have been scanned, so the call reads one int back from the
+// device (as the reference does) before it allocates the output.
+template<typename launch_arg_t = empty_t, typename a_it, typename b_it,
+  typename comp_t>
+mem_t<int2> inner_join(a_it a, int a_count, b_it b, int b_count, comp_t comp,
+  context_t& context) {
+  if(a_count <= 0 || b_count <= 0) return mem_t<int2>(0, context);
+
+  mem_t<int> lower(a_count, context);
+  mem_t<int> upper(a_count, context);
+  sorted_search<bounds_lower, launch_arg_t>(a, a_count, b, b_count,
+    lower.data(), comp, context);
+  sorted_search<bounds_upper, launch_arg_t>(a, a_count, b, b_count,
+    upper.data(), comp, context);
+
+  // Start of every a-key's run of pairs = exclusive scan of its match count.
+  mem_t<int> pair_start(a_count, context);
+  mem_t<int> pair_count(1, context);
+  const int* lower_data = lower.data();
+  const int* upper_data = upper.data();
+  transform_scan<int>([=]MGPU_DEVICE(int index) {
+    return upper_data[index] - lower_data[index];
+  }, a_count, pair_start.data(), plus_t<int>(), pair_count.data(), context);
+  int join_count = from_mem(pair_count)[0];
+
+  mem_t<int2> output(join_count, context);
+  int2* output_data = output.data();
+  transform_lbs([=]MGPU_DEVICE(int index, int seg, int rank,
+    tuple<int> first_match) {
+    output_data[index] = make_int2(seg, get<0>(first_match) + rank);
+  }, join_count, pair_start.data(), a_count, make_tuple(lower_data), context);
+  return output;
+}
+
+END_MGPU_NAMESPACE
+
+#endif // __CUDACC__

@@ -9,6 +9,8 @@
 #include <moderngpu/kernel_load_balance.hxx>
 #include <moderngpu/kernel_intervalmove.hxx>
 #include <moderngpu/kernel_scan.hxx>
+#include <moderngpu/kernel_sortedsearch.hxx>
+#include <moderngpu/kernel_join.hxx>
 
 using namespace mgpu;
 
@@ -591,6 +593,75 @@ int main() {
     report("segreduce on 16-byte values (long segments)", ok);
   }
 #endif
+
+  // 14. sorted_search, lower and upper bounds, keys with many duplicates,
+  //     against std::lower_bound / std::upper_bound (the property the
+  //     reference's tests/test_sortedsearch.cu:24-31 asserts, made exact).
+  {
+    bool ok = true;
+    const int shapes[5][3] = { { 1000, 1000, 10000 }, { 300007, 70001, 5000 },
+      { 5, 400000, 1000000 }, { 250000, 3, 50 }, { 100000, 100000, 7 } };
+    for(int c = 0; c < 5 && ok; ++c) {
+      int num_needles = shapes[c][0], num_haystack = shapes[c][1];
+      std::mt19937 rng(100 + c);
+      std::uniform_int_distribution<int> key(0, shapes[c][2]);
+      std::vector<int> needles(num_needles), haystack(num_haystack);
+      for(int& x : needles) x = key(rng);
+      for(int& x : haystack) x = key(rng);
+      std::sort(needles.begin(), needles.end());
+      std::sort(haystack.begin(), haystack.end());
+      mem_t<int> d_needles = to_mem(needles, context);
+      mem_t<int> d_haystack = to_mem(haystack, context);
+      mem_t<int> lower(num_needles, context), upper(num_needles, context);
+      sorted_search<bounds_lower>(d_needles.data(), num_needles,
+        d_haystack.data(), num_haystack, lower.data(), less_t<int>(), context);
+      sorted_search<bounds_upper>(d_needles.data(), num_needles,
+        d_haystack.data(), num_haystack, upper.data(), less_t<int>(), context);
+      std::vector<int> lo = from_mem(lower), hi = from_mem(upper);
+      for(int i = 0; i < num_needles && ok; ++i) {
+        int want_lo = (int)(std::lower_bound(haystack.begin(), haystack.end(),
+          needles[i]) - haystack.begin());
+        int want_hi = (int)(std::upper_bound(haystack.begin(), haystack.end(),
+          needles[i]) - haystack.begin());
+        ok = lo[i] == want_lo && hi[i] == want_hi;
+      }
+    }
+    report("sorted_search lower / upper bounds", ok);
+  }
+
+  // 15. inner_join against a two-pointer host join; also the empty join the
+  //     reference's tests/test_join.cu:7-8 runs.
+  {
+    bool ok = true;
+    mem_t<int2> none = inner_join((int*)nullptr, 0, (int*)nullptr, 0,
+      less_t<int>(), context);
+    ok = 0 == none.size();
+    const int shapes[3][3] = { { 200000, 150000, 60000 }, { 1000, 900000, 300 },
+      { 50000, 50000, 10000000 } };
+    for(int c = 0; c < 3 && ok; ++c) {
+      int a_count = shapes[c][0], b_count = shapes[c][1];
+      std::mt19937 rng(200 + c);
+      std::uniform_int_distribution<int> key(0, shapes[c][2]);
+      std::vector<int> a(a_count), b(b_count);
+      for(int& x : a) x = key(rng);
+      for(int& x : b) x = key(rng);
+      std::sort(a.begin(), a.end());
+      std::sort(b.begin(), b.end());
+      mem_t<int> d_a = to_mem(a, context), d_b = to_mem(b, context);
+      mem_t<int2> joined = inner_join(d_a.data(), a_count, d_b.data(), b_count,
+        less_t<int>(), context);
+      std::vector<int2> got = from_mem(joined);
+      size_t at = 0;
+      for(int i = 0; i < a_count && ok; ++i) {
+        int first = (int)(std::lower_bound(b.begin(), b.end(), a[i]) - b.begin());
+        int last = (int)(std::upper_bound(b.begin(), b.end(), a[i]) - b.begin());
+        for(int j = first; j < last && ok; ++j, ++at)
+          ok = at < got.size() && got[at].x == i && got[at].y == j;
+      }
+      ok = ok && at == got.size();
+    }
+    report("inner_join", ok);
+  }
 
   context.synchronize();
   if(failures) printf("FAILED %d\n", failures);

@@ -199,3 +199,15 @@ def test_nearest_pipeline_on_the_reference_itself():
     run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert "FAIL" not in run.stdout, run.stdout
     assert "ALL PASSED" in run.stdout, run.stdout + run.stderr
+
+
+def test_workcreate_bfs_on_the_reference_itself():
+    """tests/cpp/test_workcreate_bfs.cu compiled against the REFERENCE's
+    headers: the properties checked (levels, order of the compacted frontier,
+    segment starts) are properties of the reference's engine too."""
+    exe = os.path.join(REF_DIR, "workcreate_bfs_on_reference")
+    if not os.path.exists(exe):
+        pytest.skip("reference-built work-creation program not present")
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert "FAIL" not in run.stdout, run.stdout
+    assert "ALL PASSED" in run.stdout, run.stdout + run.stderr

@@ -37,6 +37,20 @@ def test_nearest_pipeline():
     assert run.returncode == 0
 
 
+def test_workcreate_bfs():
+    """tests/cpp/test_workcreate_bfs.cu: breadth-first search whose frontier
+    is expanded by expt::lbs_workcreate (upsweep / downsweep), the way the
+    reference's demo/bfs2.cu:23-65 uses it, on seeded synthetic graphs;
+    levels against a host search, every round's segment array against the
+    scan of the claimed vertices' degrees."""
+    run = run_program(os.path.join(ROOT, "tests", "cpp", "build",
+                                   "test_workcreate_bfs"))
+    print(run.stdout)
+    assert "FAIL" not in run.stdout, run.stdout
+    assert "ALL PASSED" in run.stdout, run.stdout + run.stderr
+    assert run.returncode == 0
+
+
 def test_template_entry_points():
     run = run_program(EXE)
     print(run.stdout)
