@@ -101,6 +101,10 @@ def fold_plan(flags, rank):
     return take
 
 
+class MailboxError(RuntimeError):
+    """The peer-to-peer mailboxes could not be set up on every rank."""
+
+
 class Mailbox:
     """This rank's mailbox and its mapping of every other rank's mailbox.
 
@@ -124,33 +128,65 @@ class Mailbox:
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.device = device
-        own = ctypes.c_void_p()
+        # Set-up is all-or-nothing across the group: a rank on which a step
+        # fails keeps taking part in the collectives below, and every rank
+        # learns of the failure from the final vote.
+        failure = None
+        self.own = None
+        self.opened = []
         handle = (ctypes.c_ubyte * 64)()
-        with torch.cuda.device(device):
-            binding._check(lib.mgpu_b200_mailbox_create(ctypes.byref(own),
-                                                        handle))
-        self.own = own.value
+        try:
+            own = ctypes.c_void_p()
+            with torch.cuda.device(device):
+                binding._check(lib.mgpu_b200_mailbox_create(ctypes.byref(own),
+                                                            handle))
+            self.own = own.value
+        except Exception as e:                      # noqa: BLE001
+            failure = e
         handles = [bytes(handle)]
         if self.world > 1:
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=group)
-        self.opened = []
+            dist.all_gather_object(
+                handles, bytes(handle) if failure is None else None,
+                group=group)
         pointers = []
-        with torch.cuda.device(device):
-            for k in range(self.world):
-                if k == self.rank:
-                    pointers.append(self.own)
-                    continue
-                peer = ctypes.c_void_p()
-                raw = (ctypes.c_ubyte * 64).from_buffer_copy(handles[k])
-                binding._check(lib.mgpu_b200_mailbox_open(raw,
-                                                          ctypes.byref(peer)))
-                self.opened.append(peer.value)
-                pointers.append(peer.value)
+        if failure is None and all(h is not None for h in handles):
+            try:
+                with torch.cuda.device(device):
+                    for k in range(self.world):
+                        if k == self.rank:
+                            pointers.append(self.own)
+                            continue
+                        peer = ctypes.c_void_p()
+                        raw = (ctypes.c_ubyte * 64).from_buffer_copy(handles[k])
+                        binding._check(lib.mgpu_b200_mailbox_open(
+                            raw, ctypes.byref(peer)))
+                        self.opened.append(peer.value)
+                        pointers.append(peer.value)
+            except Exception as e:                  # noqa: BLE001
+                failure = e
+        elif failure is None:
+            failure = MailboxError("another rank could not create its mailbox")
+        if self.world > 1:
+            vote = torch.tensor([0 if failure is None else 1], device=device,
+                                dtype=torch.int32)
+            dist.all_reduce(vote, op=dist.ReduceOp.MAX, group=group)
+            if int(vote.item()) and failure is None:
+                failure = MailboxError("another rank could not map the mailboxes")
+        if failure is not None:
+            self._release()
+            raise MailboxError("peer-to-peer mailbox set-up failed: %s"
+                               % failure)
         self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
         torch.cuda.synchronize(device)
-        if self.world > 1:
-            dist.barrier(group=group)
+
+    def _release(self):
+        with torch.cuda.device(self.device):
+            for peer in self.opened:
+                self.lib.mgpu_b200_mailbox_close(peer)
+            if self.own is not None:
+                self.lib.mgpu_b200_mailbox_destroy(self.own)
+        self.own, self.opened = None, []
 
     def next_step(self):
         self.step += 1
