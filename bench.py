@@ -519,6 +519,18 @@ def run_other_config(args, rank, world, local_rank):
         out = torch.empty_like(x)
         steps["exclusive scan int32, %d items" % n_scan] = (
             lambda: mgpu.scan(x, out=out), x.numel(), 8 * x.numel())
+    elif cfg == "search":
+        # 2^27 sorted int32 needles into a sorted haystack of 2^27 keys.
+        n_keys = 1 << (24 if args.small else 27)
+        g = torch.Generator(device=device).manual_seed(5)
+        needles = torch.sort(torch.randint(0, 1 << 30, (n_keys,), device=device,
+                                           dtype=torch.int32, generator=g))[0]
+        hay = torch.sort(torch.randint(0, 1 << 30, (n_keys,), device=device,
+                                       dtype=torch.int32, generator=g))[0]
+        found = torch.empty(n_keys, dtype=torch.int32, device=device)
+        steps["sorted_search lower bound, %d + %d int32 keys" % (n_keys, n_keys)] = (
+            lambda: mgpu.sorted_search(needles, hay, out=found), n_keys,
+            12 * n_keys)
     elif cfg == "c5":
         # The whole 2^32-item array, always as 8 shards of 2^29 items; each of
         # the N ranks holds 8/N consecutive shards (strong scaling).
@@ -608,7 +620,7 @@ def main():
                         help="2^26 items / 2^21 segments per GPU: a case "
                              "small enough for a full ncu capture")
     parser.add_argument("--config", default="c2",
-                        choices=["c1", "c2", "c3", "c4", "c5", "scan"],
+                        choices=["c1", "c2", "c3", "c4", "c5", "scan", "search"],
                         help="c2 (default) is the headline line; the others "
                              "print a shorter secondary line")
     parser.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],

@@ -93,6 +93,33 @@ sorted_search_k(needles_it needles, int num_needles, haystack_it haystack,
   }
 }
 
+// Ints of scratch the search needs for its partition table.
+template<typename tuning_t = search_default_tuning>
+inline size_t sorted_search_partitions(int num_needles, int num_haystack) {
+  return (size_t)div_up((int64_t)num_needles + num_haystack,
+    (int64_t)tuning_t::nv) + 1;
+}
+
+// Partition + search kernel on `stream`; `partitions` holds
+// sorted_search_partitions<tuning_t>(...) ints.
+template<bounds_t bounds, typename tuning_t, typename needles_it,
+  typename haystack_it, typename indices_it, typename comp_t>
+void sorted_search_enqueue(needles_it needles, int num_needles,
+  haystack_it haystack, int num_haystack, indices_it indices, comp_t comp,
+  int* partitions, cudaStream_t stream) {
+  typedef typename std::iterator_traits<needles_it>::value_type type_t;
+  if(!num_needles) return;
+  int num_tiles = (int)div_up((int64_t)num_needles + num_haystack,
+    (int64_t)tuning_t::nv);
+  int num_partitions = num_tiles + 1;
+  merge_path_partitions_k<bounds><<<div_up(num_partitions, 128), 128, 0,
+    stream>>>(needles, num_needles, haystack, num_haystack, (int)tuning_t::nv,
+    num_partitions, comp, partitions);
+  sorted_search_k<bounds, tuning_t, type_t><<<num_tiles, (int)tuning_t::nt, 0,
+    stream>>>(needles, num_needles, haystack, num_haystack, indices, comp,
+    partitions);
+}
+
 } // namespace detail
 
 // The merge-path partition table of two sorted sequences, one entry per
@@ -115,18 +142,15 @@ template<bounds_t bounds, typename launch_arg_t = empty_t,
 void sorted_search(needles_it needles, int num_needles, haystack_it haystack,
   int num_haystack, indices_it indices, comp_it comp, context_t& context) {
   typedef typename detail::pick_search_tuning<launch_arg_t>::type tuning_t;
-  typedef typename std::iterator_traits<needles_it>::value_type type_t;
   if(num_needles < 0 || num_haystack < 0 ||
     (int64_t)num_needles + num_haystack > (int64_t)0x7fffffff - 65536)
     throw cuda_exception_t(cudaErrorInvalidValue);
   if(!num_needles) return;
-  int num_tiles = (int)div_up((int64_t)num_needles + num_haystack,
-    (int64_t)tuning_t::nv);
-  mem_t<int> partitions = merge_path_partitions<bounds>(needles, num_needles,
-    haystack, num_haystack, (int64_t)tuning_t::nv, comp, context);
-  detail::sorted_search_k<bounds, tuning_t, type_t><<<num_tiles,
-    (int)tuning_t::nt, 0, context.stream()>>>(needles, num_needles, haystack,
-    num_haystack, indices, comp, partitions.data());
+  mem_t<int> partitions(detail::sorted_search_partitions<tuning_t>(
+    num_needles, num_haystack), context);
+  detail::sorted_search_enqueue<bounds, tuning_t>(needles, num_needles,
+    haystack, num_haystack, indices, comp, partitions.data(),
+    context.stream());
 }
 
 // All pairs (a_index, b_index) whose keys are equivalent under `comp`; both

@@ -190,6 +190,24 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
   const void* init_host, void* reserved);
 
 /*
+ * mgpu::sorted_search (reference: src/moderngpu/kernel_sortedsearch.hxx:7-62)
+ * with less-than: for every one of num_needles SORTED keys, the lower bound
+ * (upper == 0: number of haystack keys less than it) or the upper bound
+ * (upper != 0: number of haystack keys not greater than it) in the SORTED
+ * haystack. dtype is MGPU_B200_I32, _I64, _F32 or _F64. Workspace:
+ * mgpu_b200_sorted_search_workspace_bytes(num_needles, num_haystack),
+ * 128-byte aligned. inner_join and the other callers that need user types
+ * are in the C++ headers.
+ */
+size_t mgpu_b200_sorted_search_workspace_bytes(int num_needles,
+  int num_haystack);
+
+int mgpu_b200_sorted_search(int dtype, int upper, const void* needles_device,
+  int num_needles, const void* haystack_device, int num_haystack,
+  int* indices_device, void* workspace_device, size_t workspace_bytes,
+  void* stream);
+
+/*
  * Optional L2 residency for an array that later calls on `stream` gather from
  * at random -- the vector of mgpu_b200_spmv. No counterpart in the reference.
  * mgpu_b200_l2_pin sets aside min(bytes, the device's maximum) of this

@@ -19,6 +19,7 @@ from .binding import (  # noqa: F401
     load_library,
     scan,
     segreduce,
+    sorted_search,
     segreduce_host,
     segreduce_profile,
     segreduce_static,
@@ -30,6 +31,7 @@ from .binding import (  # noqa: F401
 __all__ = [
     "LibraryMissing", "MgpuError", "interval_expand", "l2_pin", "l2_unpin", "lib_path",
     "load_balance_partitions", "load_balance_search", "load_library", "scan",
+    "sorted_search",
     "segreduce", "segreduce_host", "segreduce_profile",
     "segreduce_static", "spmv", "transform_lbs", "workspace_status",
 ]

@@ -124,6 +124,12 @@ def _declare_optional(lib):
     lib.mgpu_b200_shard_lead.argtypes = [
         c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
         c_void_p]
+    lib.mgpu_b200_sorted_search_workspace_bytes.restype = c_size_t
+    lib.mgpu_b200_sorted_search_workspace_bytes.argtypes = [c_int, c_int]
+    lib.mgpu_b200_sorted_search.restype = c_int
+    lib.mgpu_b200_sorted_search.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_size_t, c_void_p]
     lib.mgpu_b200_l2_pin.restype = c_int
     lib.mgpu_b200_l2_pin.argtypes = [c_void_p, c_size_t, c_void_p]
     lib.mgpu_b200_l2_unpin.restype = c_int
@@ -223,6 +229,31 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
             dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
             num_segments, out.data_ptr(), ctypes.byref(init_c),
             workspace.data_ptr(), workspace.numel(), _stream(input.device)))
+    return out
+
+
+def sorted_search(needles, haystack, upper=False, out=None, workspace=None):
+    """mgpu::sorted_search with less-than: for every key of the sorted 1-D
+    CUDA tensor `needles` its lower (or upper) bound in the sorted `haystack`
+    (same dtype), as int32."""
+    lib = load_library()
+    _require_cuda(needles, "needles")
+    _require_cuda(haystack, "haystack", needles.dtype)
+    if needles.dtype not in _DTYPES:
+        raise TypeError("unsupported dtype %s" % needles.dtype)
+    if out is None:
+        out = torch.empty(needles.numel(), dtype=torch.int32,
+                          device=needles.device)
+    need = lib.mgpu_b200_sorted_search_workspace_bytes(needles.numel(),
+                                                       haystack.numel())
+    if workspace is None:
+        workspace = _workspace(needles.device, need)
+    with torch.cuda.device(needles.device):
+        _check(lib.mgpu_b200_sorted_search(
+            _DTYPES[needles.dtype], 1 if upper else 0, needles.data_ptr(),
+            needles.numel(), haystack.data_ptr(), haystack.numel(),
+            out.data_ptr(), workspace.data_ptr(), workspace.numel(),
+            _stream(needles.device)))
     return out
 
 

@@ -5,6 +5,7 @@
 #include <moderngpu/kernel_load_balance.hxx>
 #include <moderngpu/kernel_intervalmove.hxx>
 #include <moderngpu/kernel_scan.hxx>
+#include <moderngpu/kernel_sortedsearch.hxx>
 #include <mutex>
 #include <vector>
 #include <algorithm>
@@ -585,6 +586,48 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
     return MGPU_B200_E_INVALID;
   return segreduce_host_impl(dtype, op, (const char*)input_host, count,
     segments_host, num_segments, (char*)output_host, init_host);
+}
+
+size_t mgpu_b200_sorted_search_workspace_bytes(int num_needles,
+  int num_haystack) {
+  if(num_needles < 0 || num_haystack < 0) return 0;
+  return (detail::sorted_search_partitions<>(num_needles, num_haystack) *
+    sizeof(int) + 127) / 128 * 128;
+}
+
+int mgpu_b200_sorted_search(int dtype, int upper, const void* needles_device,
+  int num_needles, const void* haystack_device, int num_haystack,
+  int* indices_device, void* workspace_device, size_t workspace_bytes,
+  void* stream) {
+  if(!sizes_ok(num_needles, num_haystack)) return MGPU_B200_E_INVALID;
+  if(0 == num_needles) return MGPU_B200_OK;
+  if(!needles_device || !indices_device ||
+    (num_haystack && !haystack_device) || !workspace_device)
+    return MGPU_B200_E_INVALID;
+  if(workspace_bytes <
+    mgpu_b200_sorted_search_workspace_bytes(num_needles, num_haystack))
+    return MGPU_B200_E_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  int* partitions = (int*)workspace_device;
+  typedef detail::search_default_tuning tuning_t;
+  #define MGPU_B200_SEARCH(type_t) \
+    if(upper) detail::sorted_search_enqueue<bounds_upper, tuning_t>( \
+      (const type_t*)needles_device, num_needles, \
+      (const type_t*)haystack_device, num_haystack, indices_device, \
+      less_t<type_t>(), partitions, s); \
+    else detail::sorted_search_enqueue<bounds_lower, tuning_t>( \
+      (const type_t*)needles_device, num_needles, \
+      (const type_t*)haystack_device, num_haystack, indices_device, \
+      less_t<type_t>(), partitions, s);
+  switch(dtype) {
+    case MGPU_B200_I32: MGPU_B200_SEARCH(int) break;
+    case MGPU_B200_I64: MGPU_B200_SEARCH(long long) break;
+    case MGPU_B200_F32: MGPU_B200_SEARCH(float) break;
+    case MGPU_B200_F64: MGPU_B200_SEARCH(double) break;
+    default: return MGPU_B200_E_UNSUPPORTED;
+  }
+  #undef MGPU_B200_SEARCH
+  return last_launch_code();
 }
 
 int mgpu_b200_l2_pin(const void* array_device, size_t bytes, void* stream) {
