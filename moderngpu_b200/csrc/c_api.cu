@@ -591,7 +591,8 @@ int mgpu_b200_segreduce_host(int dtype, int op, const void* input_host,
 size_t mgpu_b200_sorted_search_workspace_bytes(int num_needles,
   int num_haystack) {
   if(num_needles < 0 || num_haystack < 0) return 0;
-  return (detail::sorted_search_partitions<>(num_needles, num_haystack) *
+  // 128-byte header (status word, as in the other calls) + partition table.
+  return 128 + (detail::sorted_search_partitions<>(num_needles, num_haystack) *
     sizeof(int) + 127) / 128 * 128;
 }
 
@@ -607,8 +608,10 @@ int mgpu_b200_sorted_search(int dtype, int upper, const void* needles_device,
   if(workspace_bytes <
     mgpu_b200_sorted_search_workspace_bytes(num_needles, num_haystack))
     return MGPU_B200_E_WORKSPACE;
+  if((uintptr_t)workspace_device % 128) return MGPU_B200_E_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
-  int* partitions = (int*)workspace_device;
+  cudaMemsetAsync(workspace_device, 0, 128, s);
+  int* partitions = (int*)((char*)workspace_device + 128);
   typedef detail::search_default_tuning tuning_t;
   #define MGPU_B200_SEARCH(type_t) \
     if(upper) detail::sorted_search_enqueue<bounds_upper, tuning_t>( \
