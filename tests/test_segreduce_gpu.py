@@ -191,3 +191,45 @@ def test_workspace_too_small_is_reported(mgpu):
     with pytest.raises(mgpu.MgpuError) as info:
         mgpu.segreduce(values, seg, workspace=tiny)
     assert info.value.code == 2
+
+
+MAX_MERGED = 0x7FFFFFFF - 65536      # count + num_segments a single call takes
+
+
+def test_maximum_size_single_call(mgpu):
+    """The largest problem one call indexes (count + num_segments =
+    2^31 - 65537, as in the reference, whose grid is sized from the same sum):
+    int32 ones, segment sums must equal the segment lengths; the load-balancing
+    search of the same shape must number every item. One item more is refused
+    with an error code instead of wrapping around."""
+    num_segments = 1_000_003
+    count = MAX_MERGED - num_segments
+    g = torch.Generator(device="cuda").manual_seed(8)
+    cuts = torch.randint(0, count, (num_segments - 1,), device="cuda", generator=g)
+    segments = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"),
+                          torch.sort(cuts)[0]]).to(torch.int32)
+    del cuts
+    values = torch.ones(count, dtype=torch.int32, device="cuda")
+    out = mgpu.segreduce(values, segments, op="plus", init=-5)
+    ends = torch.cat([segments[1:], torch.tensor([count], dtype=torch.int32, device="cuda")])
+    lengths = ends - segments
+    want = torch.where(lengths > 0, lengths, torch.full_like(lengths, -5))
+    assert torch.equal(out, want)
+    assert mgpu.workspace_status() == 0
+    del values, out
+
+    seg = mgpu.load_balance_search(count, segments)
+    # Every item's segment starts at or before it and the next one after it;
+    # checked in slices to keep the temporaries small.
+    step = 1 << 28
+    for lo in range(0, count, step):
+        hi = min(lo + step, count)
+        index = torch.arange(lo, hi, device="cuda", dtype=torch.int64)
+        s = seg[lo:hi].to(torch.int64)
+        assert bool((segments[s].to(torch.int64) <= index).all())
+        assert bool((ends[s].to(torch.int64) > index).all())
+    del seg
+
+    too_many = torch.empty(count + 1, dtype=torch.int32, device="cuda")
+    with pytest.raises(mgpu.MgpuError):
+        mgpu.segreduce(too_many, segments, op="plus", init=0)
