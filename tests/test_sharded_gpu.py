@@ -228,3 +228,79 @@ def test_mailbox_waits_are_bounded(mgpu):
     # The context still works.
     again = mgpu.segreduce(v, t, op="plus", init=0)
     assert torch.equal(again, before)
+
+
+def stall_worker(rank, world, port, queue):
+    """Step 1: every rank takes part. Step 2: the last rank stalls (posts
+    nothing, collects nothing, stays alive). Step 3: every rank again."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        values, seg = make_problem("few_long", np.int64)
+        begin, end, first, table = sharded.shard_table(seg, values.size, rank, world)
+        v = torch.from_numpy(values[begin:end].copy()).cuda()
+        t = torch.from_numpy(table).cuda()
+        box = sharded.Mailbox(timeout_ns=20_000_000)          # 20 ms
+        report = {}
+        for step in (1, 2, 3):
+            if step == 2 and rank == world - 1:
+                box.next_step()                 # the stalled rank skips the step
+                out = None
+            else:
+                out = sharded.sharded_segreduce(v, t, op="plus", init=-7, mailbox=box)
+            torch.cuda.synchronize()
+            report[step] = (box.status(),
+                            None if out is None else out.cpu().numpy().tolist())
+            dist.barrier()
+        box.close()
+        pieces = [None] * world
+        dist.all_gather_object(pieces, (first, report))
+        if rank == 0:
+            queue.put(pieces)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_a_stalled_rank_is_detected_not_waited_for(oracle):
+    """Failure detection without a GPU fault: when a rank posts no record for
+    a step, the rank that owns the straddling segment gives up after its time
+    limit, reports status 3 through its mailbox, leaves its own result
+    unfolded, and the next step works again. Plain peer stores, NVLS off; no
+    process exits while another may still write to it."""
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=stall_worker, args=(r, world, port, queue))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    pieces = queue.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    values, seg = make_problem("few_long", np.int64)
+    want = oracle.segreduce(values, seg.astype(np.int32), op="plus", init=-7)
+    (first0, rep0), (first1, rep1) = pieces
+    # Steps 1 and 3: the assembled result is the whole array's reduction.
+    for step in (1, 3):
+        got = np.zeros(seg.size, dtype=np.int64)
+        for first, rep in pieces:
+            vals = rep[step][1][1:]
+            got[first:first + len(vals)] = vals
+        assert np.array_equal(got, want)
+    assert rep0[1][0] == 0
+    # Step 2 on rank 0: timed out waiting for rank 1's record, said so, and
+    # kept the reduction of its own items in the straddling segment.
+    assert rep0[2][0] == 3
+    half = values.size // 2
+    last_start = int(seg[seg < half][-1])      # rank 0's straddling segment
+    own_part = int(values[last_start:half].sum())
+    assert rep0[2][1][-1] == own_part
+    assert rep1[2][1] is None
