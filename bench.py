@@ -519,6 +519,18 @@ def run_other_config(args, rank, world, local_rank):
         out = torch.empty_like(x)
         steps["exclusive scan int32, %d items" % n_scan] = (
             lambda: mgpu.scan(x, out=out), x.numel(), 8 * x.numel())
+    elif cfg == "lbs_segreduce":
+        # Config 2's items and segments through lbs_segreduce: the functor
+        # reads values[index] and multiplies by a weight cached per segment.
+        values, seg, _ = make_shard(0, device)
+        g = torch.Generator(device=device).manual_seed(11)
+        weights = torch.rand(seg.numel(), device=device, generator=g)
+        out = torch.empty(seg.numel(), dtype=torch.float32, device=device)
+        steps["lbs_segreduce fp32 weighted sums, config 2 shape"] = (
+            lambda: mgpu.lbs_segreduce_weighted(values, seg, weights, out=out),
+            values.numel(),
+            workloads.segreduce_bytes(values.numel(), seg.numel(), 4)
+            + 4 * seg.numel())
     elif cfg == "search":
         # 2^27 sorted int32 needles into a sorted haystack of 2^27 keys.
         n_keys = 1 << (24 if args.small else 27)
@@ -620,7 +632,8 @@ def main():
                         help="2^26 items / 2^21 segments per GPU: a case "
                              "small enough for a full ncu capture")
     parser.add_argument("--config", default="c2",
-                        choices=["c1", "c2", "c3", "c4", "c5", "scan", "search"],
+                        choices=["c1", "c2", "c3", "c4", "c5", "scan", "search",
+                                 "lbs_segreduce"],
                         help="c2 (default) is the headline line; the others "
                              "print a shorter secondary line")
     parser.add_argument("--exchange", default="p2p", choices=["p2p", "nccl"],

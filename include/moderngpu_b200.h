@@ -149,6 +149,23 @@ int mgpu_b200_spmv(int dtype, const void* matrix_device,
   void* workspace_device, size_t workspace_bytes, void* stream);
 
 /*
+ * mgpu::lbs_segreduce (reference: src/moderngpu/kernel_segreduce.hxx:303-387)
+ * with the functor f(index, seg, rank, tuple<weight>) = values[index] * weight,
+ * the weight cached per segment (caching_iterators = tuple<weights>), op plus,
+ * init 0:  output[s] = sum over the items i of segment s of
+ * values[i] * weights[s]; 0 for an empty segment. The load-balancing search
+ * that finds every item's segment is fused into the reduction. dtype is
+ * MGPU_B200_F32 or MGPU_B200_F64. Other functors: the C++ header.
+ */
+size_t mgpu_b200_lbs_segreduce_weighted_workspace_bytes(int dtype, int count,
+  int num_segments);
+
+int mgpu_b200_lbs_segreduce_weighted(int dtype, const void* values_device,
+  int count, const int* segments_device, int num_segments,
+  const void* weights_device, void* output_device, void* workspace_device,
+  size_t workspace_bytes, void* stream);
+
+/*
  * mgpu::transform_lbs (reference: src/moderngpu/kernel_load_balance.hxx:8-76)
  * with the functor that records its arguments: for every item index in
  * [0, count), seg_out[index] = (number of segment starts <= index) - 1 and,

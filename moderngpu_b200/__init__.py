@@ -13,6 +13,7 @@ from .binding import (  # noqa: F401
     interval_expand,
     l2_pin,
     l2_unpin,
+    lbs_segreduce_weighted,
     lib_path,
     load_balance_partitions,
     load_balance_search,
@@ -29,7 +30,7 @@ from .binding import (  # noqa: F401
 )
 
 __all__ = [
-    "LibraryMissing", "MgpuError", "interval_expand", "l2_pin", "l2_unpin", "lib_path",
+    "LibraryMissing", "MgpuError", "interval_expand", "l2_pin", "l2_unpin", "lbs_segreduce_weighted", "lib_path",
     "load_balance_partitions", "load_balance_search", "load_library", "scan",
     "sorted_search",
     "segreduce", "segreduce_host", "segreduce_profile",

@@ -124,6 +124,13 @@ def _declare_optional(lib):
     lib.mgpu_b200_shard_lead.argtypes = [
         c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
         c_void_p]
+    lib.mgpu_b200_lbs_segreduce_weighted_workspace_bytes.restype = c_size_t
+    lib.mgpu_b200_lbs_segreduce_weighted_workspace_bytes.argtypes = [
+        c_int, c_int, c_int]
+    lib.mgpu_b200_lbs_segreduce_weighted.restype = c_int
+    lib.mgpu_b200_lbs_segreduce_weighted.argtypes = [
+        c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+        c_size_t, c_void_p]
     lib.mgpu_b200_sorted_search_workspace_bytes.restype = c_size_t
     lib.mgpu_b200_sorted_search_workspace_bytes.argtypes = [c_int, c_int]
     lib.mgpu_b200_sorted_search.restype = c_int
@@ -229,6 +236,36 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
             dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
             num_segments, out.data_ptr(), ctypes.byref(init_c),
             workspace.data_ptr(), workspace.numel(), _stream(input.device)))
+    return out
+
+
+def lbs_segreduce_weighted(values, segments, weights, out=None,
+                           workspace=None):
+    """mgpu::lbs_segreduce with f(index, seg, rank, (weight,)) =
+    values[index] * weight and the weights cached per segment:
+    out[s] = sum of values[i] * weights[s] over segment s (0 when empty)."""
+    lib = load_library()
+    _require_cuda(values, "values")
+    _require_cuda(segments, "segments", torch.int32)
+    _require_cuda(weights, "weights", values.dtype)
+    if values.dtype not in (torch.float32, torch.float64):
+        raise TypeError("unsupported dtype %s" % values.dtype)
+    count, num_segments = values.numel(), segments.numel()
+    if weights.numel() != num_segments:
+        raise ValueError("one weight per segment")
+    if out is None:
+        out = torch.empty(num_segments, dtype=values.dtype,
+                          device=values.device)
+    dtype = _DTYPES[values.dtype]
+    need = lib.mgpu_b200_lbs_segreduce_weighted_workspace_bytes(
+        dtype, count, num_segments)
+    if workspace is None:
+        workspace = _workspace(values.device, need)
+    with torch.cuda.device(values.device):
+        _check(lib.mgpu_b200_lbs_segreduce_weighted(
+            dtype, values.data_ptr(), count, segments.data_ptr(),
+            num_segments, weights.data_ptr(), out.data_ptr(),
+            workspace.data_ptr(), workspace.numel(), _stream(values.device)))
     return out
 
 

@@ -6,6 +6,7 @@
 #include <moderngpu/kernel_intervalmove.hxx>
 #include <moderngpu/kernel_scan.hxx>
 #include <moderngpu/kernel_sortedsearch.hxx>
+#include <moderngpu/b200/lbs_segreduce.hxx>
 #include <mutex>
 #include <vector>
 #include <algorithm>
@@ -97,6 +98,49 @@ int spmv_typed(const void* matrix, const int* columns, const void* x, int nnz,
     detail::segreduce_enqueue<tuning_t>(source, nnz, row_starts, rows,
       (type_t*)y, plus_t<type_t>(), (type_t)0, workspace, stream,
       g_timeout_ns);
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
+  }
+  return last_launch_code();
+}
+
+// lbs_segreduce with a cached per-segment weight:
+// f(index, seg, rank, tuple<weight>) = values[index] * weight.
+template<typename type_t>
+struct weighted_item_t {
+  const type_t* values;
+  MGPU_DEVICE type_t operator()(int index, int seg, int rank,
+    tuple<type_t> weight) const {
+    return values[index] * get<0>(weight);
+  }
+};
+
+template<typename type_t>
+struct weighted_types {
+  typedef typename detail::lbs_segreduce_default_tuning<type_t>::type tuning_t;
+  typedef detail::lbs_source_t<weighted_item_t<type_t>,
+    tuple<const type_t*>, type_t> source_t;
+};
+
+template<typename type_t>
+size_t weighted_bytes(int count, int num_segments) {
+  detail::segreduce_plan_t<typename weighted_types<type_t>::tuning_t, type_t>
+    plan(count, num_segments);
+  return plan.bytes;
+}
+
+template<typename type_t>
+int weighted_typed(const void* values, int count, const int* segments,
+  int num_segments, const void* weights, void* output, void* workspace,
+  cudaStream_t stream) {
+  typedef weighted_types<type_t> types;
+  typename types::source_t source { weighted_item_t<type_t> {
+    (const type_t*)values }, make_tuple((const type_t*)weights),
+    tuple<>() };
+  try {
+    detail::segreduce_enqueue<typename types::tuning_t>(source, count,
+      segments, num_segments, (type_t*)output, plus_t<type_t>(), (type_t)0,
+      workspace, stream, g_timeout_ns);
   } catch(cuda_exception_t& e) {
     return cuda_code(e.result);
   }
@@ -522,6 +566,37 @@ int mgpu_b200_spmv(int dtype, const void* matrix_device,
       nnz, row_starts_device, rows, y_device, workspace_device, s);
   return spmv_typed<double>(matrix_device, columns_device, vector_device, nnz,
     row_starts_device, rows, y_device, workspace_device, s);
+}
+
+size_t mgpu_b200_lbs_segreduce_weighted_workspace_bytes(int dtype, int count,
+  int num_segments) {
+  if(!sizes_ok(count, num_segments)) return 0;
+  if(MGPU_B200_F32 == dtype) return weighted_bytes<float>(count, num_segments);
+  if(MGPU_B200_F64 == dtype) return weighted_bytes<double>(count, num_segments);
+  return 0;
+}
+
+int mgpu_b200_lbs_segreduce_weighted(int dtype, const void* values_device,
+  int count, const int* segments_device, int num_segments,
+  const void* weights_device, void* output_device, void* workspace_device,
+  size_t workspace_bytes, void* stream) {
+  if(!sizes_ok(count, num_segments)) return MGPU_B200_E_INVALID;
+  if(0 == count + num_segments) return MGPU_B200_OK;
+  if((count && !values_device) ||
+    (num_segments && (!segments_device || !weights_device || !output_device)) ||
+    !workspace_device || (uintptr_t)workspace_device % 128)
+    return MGPU_B200_E_INVALID;
+  if(MGPU_B200_F32 != dtype && MGPU_B200_F64 != dtype)
+    return MGPU_B200_E_UNSUPPORTED;
+  if(workspace_bytes <
+    mgpu_b200_lbs_segreduce_weighted_workspace_bytes(dtype, count, num_segments))
+    return MGPU_B200_E_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  if(MGPU_B200_F32 == dtype)
+    return weighted_typed<float>(values_device, count, segments_device,
+      num_segments, weights_device, output_device, workspace_device, s);
+  return weighted_typed<double>(values_device, count, segments_device,
+    num_segments, weights_device, output_device, workspace_device, s);
 }
 
 size_t mgpu_b200_lbs_workspace_bytes(int count, int num_segments) {

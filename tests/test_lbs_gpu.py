@@ -118,3 +118,24 @@ def test_config4_full_size_properties(mgpu):
                                             dtype=torch.int32)])[ids.long()]
     assert bool((index < ends).all())
     assert bool((ids[1:] >= ids[:-1]).all())
+
+
+@pytest.mark.parametrize("count,num_segments", [(0, 5), (1, 1), (1000, 37), (1_000_003, 30_011),
+                                                (5_000_000, 11), (70_000, 200_000)])
+def test_lbs_segreduce_weighted_is_exact_on_small_integers(mgpu, oracle, count, num_segments):
+    """mgpu::lbs_segreduce through the C ABI (values[index] * weight cached per
+    segment, plus, init 0). Small integer values and power-of-two weights keep
+    every product and partial sum exact in fp32, so the result must equal the
+    oracle's segment sums times the weights bit for bit."""
+    rng = np.random.default_rng(count + num_segments)
+    values = rng.integers(-8, 9, size=count).astype(np.float32)
+    seg = np.zeros(num_segments, dtype=np.int32)
+    if num_segments > 1:
+        seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    weights = (2.0 ** rng.integers(-2, 3, size=num_segments)).astype(np.float32)
+    got = mgpu.lbs_segreduce_weighted(torch.from_numpy(values).cuda(),
+                                      torch.from_numpy(seg).cuda(),
+                                      torch.from_numpy(weights).cuda()).cpu().numpy()
+    sums = oracle.segreduce(values.astype(np.float64), seg, op="plus", init=0.0)
+    assert np.array_equal(got.astype(np.float64), sums * weights)
+    assert mgpu.workspace_status() == 0
