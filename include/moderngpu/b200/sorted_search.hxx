@@ -19,8 +19,8 @@
 // haystack keys came before; the bounds leave through shared memory in
 // coalesced stores. (A binary search per needle over the staged haystack
 // range, the first version: 0.77 ms for 2^27 + 2^27 int32 keys; this one
-// 0.63 ms = 2.5 TB/s. What is left is the unhidden load-merge-store sequence
-// of one small tile per CTA; the kernel does not prefetch.)
+// 0.63 ms, and 0.55 ms = 2.9 TB/s in the streaming variant below, which
+// prefetches.)
 #pragma once
 #include "partition.hxx"
 #include "scan.hxx"
@@ -37,7 +37,8 @@ struct search_tuning_t {
 
 namespace detail {
 
-// 256 x 15 measured best of nine shapes (2^27 + 2^27 int32 keys: 632 us).
+// 256 x 15 measured best of nine shapes (2^27 + 2^27 int32 keys: 550 us with
+// the streaming kernel, 632 us with one CTA per tile).
 typedef search_tuning_t<256, 15> search_default_tuning;
 
 template<typename launch_arg_t>
@@ -122,6 +123,173 @@ sorted_search_k(needles_it needles, int num_needles, haystack_it haystack,
   for(int i = tid; i < na; i += nt) indices[a0 + i] = found[i];
 }
 
+////////////////////////////////////////////////////////////////////////////////
+// Streaming variant for 4- and 8-byte arithmetic keys behind 16-byte aligned
+// raw pointers. The kernel above loads, merges and stores one small tile per
+// CTA in sequence, so most of a CTA's life is spent waiting for its loads.
+// Here a persistent CTA walks its tiles while one producer lane stages the
+// needle and haystack windows of the tiles ahead with bulk asynchronous
+// copies; the consumers only ever wait for shared memory.
+
+struct search_window_t {
+  int a0, a1, b0, b1;          // needles [a0, a1), haystack keys [b0, b1)
+  int a_slot, b_slot;          // shared-memory element index of a0 and of b0
+  int a_bulk, b_bulk;          // first needle / key index NOT delivered by
+                               // the bulk copies (the ragged end of an array)
+};
+
+template<typename tuning_t, int stages, typename type_t>
+struct search_stream_smem_t {
+  enum { nv = tuning_t::nv, per16 = 16 / (int)sizeof(type_t),
+    key_slots = nv + 4 * per16 };
+  alignas(128) type_t keys[stages][key_slots];
+  int found[2][nv];
+  search_window_t window[stages];
+  uint64_t full[stages], empty[stages];
+};
+
+template<bounds_t bounds, typename tuning_t, int stages, typename type_t,
+  typename indices_it, typename comp_t>
+__global__ void __launch_bounds__(tuning_t::nt + 32)
+sorted_search_stream_k(const type_t* needles, int num_needles,
+  const type_t* haystack, int num_haystack, indices_it indices, comp_t comp,
+  const int* partitions, int num_tiles) {
+  enum { nt = tuning_t::nt, vt = tuning_t::vt, nv = tuning_t::nv,
+    warps = nt / 32, per16 = 16 / (int)sizeof(type_t) };
+  typedef search_stream_smem_t<tuning_t, stages, type_t> smem_t;
+  extern __shared__ __align__(128) char search_raw[];
+  smem_t& shared = *reinterpret_cast<smem_t*>(search_raw);
+  const uint64_t timeout_ns = 2000000000ull;
+
+  const int tid = (int)threadIdx.x;
+  if(0 == tid) {
+    for(int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&shared.full[s], 1);
+      ptx::mbar_init(&shared.empty[s], nt);
+    }
+    ptx::fence_proxy_async();
+  }
+  __syncthreads();
+
+  const int first_tile = (int)blockIdx.x, step = (int)gridDim.x;
+  const int my_tiles = first_tile < num_tiles ?
+    (num_tiles - first_tile + step - 1) / step : 0;
+  const long long total = (long long)num_needles + num_haystack;
+
+  if(tid >= nt) {
+    //////////////////////////////////////////////////////////////////////////
+    // Producer lane.
+    if(tid > nt || !my_tiles) return;
+    // Window of array elements [x0, x1): the whole 16-byte granules inside
+    // the array that cover it. c_lo: first element copied; bytes: size of the
+    // copy (0: none); bulk_end: first index the copy does not deliver.
+    auto plan_window = [&](int n, int x0, int x1, int& c_lo, uint32_t& bytes,
+      int& bulk_end) {
+      c_lo = x0 / per16 * per16;
+      int c_hi = (x1 + per16 - 1) / per16 * per16;
+      int inner = n / per16 * per16;
+      if(c_hi > inner) c_hi = inner;
+      bytes = 0;
+      bulk_end = x0;
+      if(x1 > x0 && c_hi > c_lo) {
+        bytes = (uint32_t)(c_hi - c_lo) * (uint32_t)sizeof(type_t);
+        bulk_end = c_hi < x1 ? c_hi : x1;
+      }
+    };
+    int p0 = partitions[first_tile], p1 = partitions[first_tile + 1];
+    for(int k = 0; k < my_tiles; ++k) {
+      const int tile = first_tile + k * step;
+      const int s = k % stages;
+      int q0 = 0, q1 = 0;
+      if(k + 1 < my_tiles) {
+        q0 = partitions[tile + step];
+        q1 = partitions[tile + step + 1];
+      }
+      if(k >= stages &&
+        !ptx::mbar_wait(&shared.empty[s], ((k / stages) - 1) & 1, timeout_ns))
+        return;
+      const long long d0 = (long long)tile * nv;
+      const long long d1 = d0 + nv < total ? d0 + nv : total;
+      search_window_t w;
+      w.a0 = p0; w.a1 = p1;
+      w.b0 = (int)(d0 - p0); w.b1 = (int)(d1 - p1);
+      int a_lo, b_lo;
+      uint32_t a_bytes, b_bytes;
+      plan_window(num_needles, w.a0, w.a1, a_lo, a_bytes, w.a_bulk);
+      plan_window(num_haystack, w.b0, w.b1, b_lo, b_bytes, w.b_bulk);
+      type_t* a_dst = shared.keys[s];
+      // The haystack window follows the needles' slots, on a 16-byte line.
+      int a_span = (w.a0 - a_lo) + (w.a1 - w.a0);
+      type_t* b_dst = a_dst + (a_span + per16 - 1) / per16 * per16;
+      w.a_slot = w.a0 - a_lo;
+      w.b_slot = (int)(b_dst - a_dst) + (w.b0 - b_lo);
+      // The consumers read the descriptor after the barrier: write it first.
+      shared.window[s] = w;
+      ptx::fence_proxy_async();
+      if(a_bytes + b_bytes) {
+        ptx::mbar_arrive_expect_tx(&shared.full[s], a_bytes + b_bytes);
+        if(a_bytes)
+          ptx::bulk_load(a_dst, needles + a_lo, a_bytes, &shared.full[s]);
+        if(b_bytes)
+          ptx::bulk_load(b_dst, haystack + b_lo, b_bytes, &shared.full[s]);
+      } else
+        ptx::mbar_arrive(&shared.full[s]);
+      p0 = q0; p1 = q1;
+    }
+    return;
+  }
+
+  ////////////////////////////////////////////////////////////////////////////
+  // Consumers.
+  auto needle_first = [&](const type_t& a, const type_t& b) {
+    return (bounds_upper == bounds) ? comp(a, b) : !comp(b, a);
+  };
+  for(int k = 0; k < my_tiles; ++k) {
+    const int s = k % stages;
+    bool arrived = ptx::mbar_wait(&shared.full[s], (k / stages) & 1, timeout_ns);
+    const search_window_t w = shared.window[s];
+    type_t* ka = shared.keys[s] + w.a_slot;
+    type_t* kb = shared.keys[s] + w.b_slot;
+    const int na = w.a1 - w.a0, nb = w.b1 - w.b0;
+    // The ragged ends of the arrays (at most per16 - 1 elements each) come
+    // by plain loads.
+    for(int i = w.a_bulk - w.a0 + tid; i < na; i += nt) ka[i] = needles[w.a0 + i];
+    for(int i = w.b_bulk - w.b0 + tid; i < nb; i += nt) kb[i] = haystack[w.b0 + i];
+    if(!ptx::named_all<1, nt>(arrived)) return;
+
+    int* found = shared.found[k & 1];
+    const int diag = min(tid * vt, na + nb);
+    int lo = diag > nb ? diag - nb : 0, hi = diag < na ? diag : na;
+    while(lo < hi) {
+      int mid = (lo + hi) >> 1;
+      if(needle_first(ka[mid], kb[diag - 1 - mid])) lo = mid + 1;
+      else hi = mid;
+    }
+    int ai = lo, bi = diag - lo;
+    type_t a_key = ai < na ? ka[ai] : type_t();
+    type_t b_key = bi < nb ? kb[bi] : type_t();
+    #pragma unroll
+    for(int i = 0; i < vt; ++i) {
+      if(diag + i < na + nb) {
+        bool take_needle = bi >= nb || (ai < na && needle_first(a_key, b_key));
+        if(take_needle) {
+          found[ai] = w.b0 + bi;
+          ++ai;
+          if(ai < na) a_key = ka[ai];
+        } else {
+          ++bi;
+          if(bi < nb) b_key = kb[bi];
+        }
+      }
+    }
+    // The keys are no longer needed: the producer may refill the stage while
+    // the bounds are being written out.
+    ptx::mbar_arrive(&shared.empty[s]);
+    ptx::named_sync<1, nt>();
+    for(int i = tid; i < na; i += nt) indices[w.a0 + i] = found[i];
+  }
+}
+
 // Ints of scratch the search needs for its partition table.
 template<typename tuning_t = search_default_tuning>
 inline size_t sorted_search_partitions(int num_needles, int num_haystack) {
@@ -144,6 +312,42 @@ void sorted_search_enqueue(needles_it needles, int num_needles,
   merge_path_partitions_k<bounds><<<div_up(num_partitions, 128), 128, 0,
     stream>>>(needles, num_needles, haystack, num_haystack, (int)tuning_t::nv,
     num_partitions, comp, partitions);
+  constexpr bool streamable =
+    std::is_pointer<needles_it>::value && std::is_pointer<haystack_it>::value &&
+    std::is_arithmetic<type_t>::value &&
+    (4 == sizeof(type_t) || 8 == sizeof(type_t)) &&
+    std::is_same<typename std::remove_cv<typename std::remove_pointer<
+      haystack_it>::type>::type, type_t>::value;
+  if constexpr (streamable) {
+    if(0 == ((uintptr_t)needles | (uintptr_t)haystack) % 16) {
+      enum { stages = 2 };
+      typedef search_stream_smem_t<tuning_t, stages, type_t> smem_t;
+      auto kernel = sorted_search_stream_k<bounds, tuning_t, stages, type_t,
+        indices_it, comp_t>;
+      const int threads = (int)tuning_t::nt + 32;
+      const int smem = (int)sizeof(smem_t);
+      static int resident[64] = { };
+      int device = 0;
+      throw_on_error(cudaGetDevice(&device));
+      int grid = device < 64 ? resident[device] : 0;
+      if(!grid) {
+        throw_on_error(cudaFuncSetAttribute(kernel,
+          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        int per_sm = 0, sms = 0;
+        throw_on_error(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm,
+          kernel, threads, smem));
+        throw_on_error(cudaDeviceGetAttribute(&sms,
+          cudaDevAttrMultiProcessorCount, device));
+        grid = per_sm * sms > 0 ? per_sm * sms : 1;
+        if(device < 64) resident[device] = grid;
+      }
+      if(grid > num_tiles) grid = num_tiles;
+      kernel<<<grid, threads, smem, stream>>>((const type_t*)needles,
+        num_needles, (const type_t*)haystack, num_haystack, indices, comp,
+        partitions, num_tiles);
+      return;
+    }
+  }
   sorted_search_k<bounds, tuning_t, type_t><<<num_tiles, (int)tuning_t::nt, 0,
     stream>>>(needles, num_needles, haystack, num_haystack, indices, comp,
     partitions);
