@@ -330,7 +330,7 @@ def run_ours(args, rank, world, local_rank):
     mailbox = None
     if world > 1 and args.exchange == "p2p":
         try:
-            mailbox = sharded.Mailbox()
+            mailbox = sharded.Mailbox(side_stream=not args.no_side_stream)
         except sharded.MailboxError as e:
             # All ranks fail together; the records then travel by all-gather.
             print("bench: %s; using --exchange nccl" % e, file=sys.stderr)
@@ -640,6 +640,10 @@ def main():
                         help="multi-GPU boundary records: peer-to-peer "
                              "stores into mailboxes (default) or an NCCL "
                              "all-gather")
+    parser.add_argument("--no-side-stream", action="store_true",
+                        help="multi-GPU, p2p: post the boundary records on "
+                             "the main stream, in front of the reduction, "
+                             "instead of on a side stream beside it")
     parser.add_argument("--impl", default="ours",
                         choices=["ours", "reference", "reference-cuda"])
     args = parser.parse_args()

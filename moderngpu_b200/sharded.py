@@ -111,11 +111,13 @@ class Mailbox:
     Collective over `group`: every rank constructs one at the same time (the
     64-byte handles travel through the process group once, at set-up; no
     collective runs in the data path afterwards). shards_per_gpu: how many
-    consecutive shards of the chain each rank holds. Use one Mailbox per
-    stream, call `close()` (collective) when done."""
+    consecutive shards of the chain each rank holds. side_stream: post the
+    records on a stream of the mailbox's own, forked from and joined to the
+    caller's stream by events. Use one Mailbox per stream, call `close()`
+    (collective) when done."""
 
     def __init__(self, group=None, shards_per_gpu=1, device=None,
-                 timeout_ns=0):
+                 timeout_ns=0, side_stream=True):
         lib = binding.load_library()
         self.lib = lib
         self.group = group
@@ -178,6 +180,11 @@ class Mailbox:
             raise MailboxError("peer-to-peer mailbox set-up failed: %s"
                                % failure)
         self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
+        self.side = self.fork = self.join = None
+        if side_stream:
+            self.side = torch.cuda.Stream(device=device)
+            self.fork = torch.cuda.Event()
+            self.join = torch.cuda.Event()
         torch.cuda.synchronize(device)
 
     def _release(self):
@@ -306,16 +313,31 @@ def _sharded_mailbox(shards, op, init, outs, workspace, mailbox):
     init_c = binding._CTYPES[shards[0][0].dtype](init)
     results = []
     with torch.cuda.device(dev):
+        # The posts depend on nothing the reductions produce: on the mailbox's
+        # side stream (the default) they run beside the partitioner and the
+        # first tiles instead of in front of them (2 GPUs: 202.3 -> 196.9 us
+        # per step).
+        side = mailbox.side
+        post_stream = stream
+        if side is not None:
+            mailbox.fork.record(torch.cuda.current_stream(dev))
+            side.wait_event(mailbox.fork)
+            post_stream = ctypes.c_void_p(side.cuda_stream)
         for j, (values, table) in enumerate(shards):
             binding._check(lib.mgpu_b200_shard_post(
                 dtype, binding._OPS[op], values.data_ptr(), values.numel(),
                 table.data_ptr(), table.numel(), mailbox.own,
                 mailbox.peers.data_ptr(), first + j, mailbox.num_shards, k,
-                step, mailbox.timeout_ns, stream))
+                step, mailbox.timeout_ns, post_stream))
+        if side is not None:
+            mailbox.join.record(side)
         for j, (values, table) in enumerate(shards):
             results.append(binding.segreduce(
                 values, table, op=op, init=init,
                 out=None if outs is None else outs[j], workspace=workspace))
+        if side is not None:
+            # The collects read this GPU's own records too.
+            torch.cuda.current_stream(dev).wait_event(mailbox.join)
         for j, (values, table) in enumerate(shards):
             binding._check(lib.mgpu_b200_shard_collect(
                 dtype, binding._OPS[op], mailbox.own,
