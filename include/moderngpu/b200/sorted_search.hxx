@@ -19,8 +19,8 @@
 // haystack keys came before; the bounds leave through shared memory in
 // coalesced stores. (A binary search per needle over the staged haystack
 // range, the first version: 0.77 ms for 2^27 + 2^27 int32 keys; this one
-// 0.63 ms, and 0.55 ms = 2.9 TB/s in the streaming variant below, which
-// prefetches.)
+// 0.63 ms, 0.55 ms in the streaming variant below, which prefetches, and
+// 0.48 ms = 3.3 TB/s once the merge walk was written without branches.)
 #pragma once
 #include "partition.hxx"
 #include "scan.hxx"
@@ -37,8 +37,9 @@ struct search_tuning_t {
 
 namespace detail {
 
-// 256 x 15 measured best of nine shapes (2^27 + 2^27 int32 keys: 550 us with
-// the streaming kernel, 632 us with one CTA per tile).
+// 256 x 15: 2^27 + 2^27 int32 keys in 483 us with the streaming kernel
+// (256 x 23: 467 us, but its tiles of 8-byte keys no longer fit the 48 KB of
+// static shared memory of the one-CTA-per-tile kernel).
 typedef search_tuning_t<256, 15> search_default_tuning;
 
 template<typename launch_arg_t>
@@ -61,6 +62,36 @@ __global__ void merge_path_partitions_k(a_it a, int a_count, b_it b,
   partitions[k] = merge_path<bounds>(a, a_count, b, b_count, (int)diag, comp);
 }
 
+// One thread's share of a tile's merge: vt steps from (ai, diag - ai). The
+// walk is written without branches -- which side is taken only selects
+// addresses and values -- because the threads of a warp take different sides
+// at every step (with branches a third of the issue slots went to divergence
+// and the kernel was bound by instruction issue). Both key runs live in one
+// shared array, so the one reload per step is a single load from a selected
+// address; a load one element past a run reads a neighbour or padding and is
+// never used.
+template<int vt, typename type_t, typename first_t>
+MGPU_DEVICE void serial_search_merge(const type_t* ka, int na,
+  const type_t* kb, int nb, int ai, int diag, int b0, int* found,
+  first_t needle_first) {
+  int bi = diag - ai;
+  int steps = na + nb - diag;
+  type_t a_key = ka[ai < na ? ai : 0];
+  type_t b_key = kb[bi < nb ? bi : 0];
+  #pragma unroll
+  for(int i = 0; i < vt; ++i) {
+    bool active = i < steps;
+    bool take_needle = bi >= nb || (ai < na && needle_first(a_key, b_key));
+    if(active && take_needle) found[ai] = b0 + bi;
+    ai += active && take_needle;
+    bi += active && !take_needle;
+    const type_t* next = take_needle ? ka + ai : kb + bi;
+    type_t key = *next;
+    a_key = take_needle ? key : a_key;
+    b_key = take_needle ? b_key : key;
+  }
+}
+
 template<bounds_t bounds, typename tuning_t, typename type_t,
   typename needles_it, typename haystack_it, typename indices_it,
   typename comp_t>
@@ -68,7 +99,8 @@ __global__ void __launch_bounds__(tuning_t::nt)
 sorted_search_k(needles_it needles, int num_needles, haystack_it haystack,
   int num_haystack, indices_it indices, comp_t comp, const int* partitions) {
   enum { nt = tuning_t::nt, vt = tuning_t::vt, nv = tuning_t::nv };
-  __shared__ type_t keys[nv];     // the tile's needles, then its haystack keys
+  __shared__ type_t keys[nv + 1]; // the tile's needles, then its haystack
+                                  // keys, and one slot the merge may read past
   __shared__ int found[nv];       // per needle of the tile
 
   const int tid = (int)threadIdx.x;
@@ -102,23 +134,7 @@ sorted_search_k(needles_it needles, int num_needles, haystack_it haystack,
     if(needle_first(ka[mid], kb[diag - 1 - mid])) lo = mid + 1;
     else hi = mid;
   }
-  int ai = lo, bi = diag - lo;
-  type_t a_key = ai < na ? ka[ai] : type_t();
-  type_t b_key = bi < nb ? kb[bi] : type_t();
-  #pragma unroll
-  for(int i = 0; i < vt; ++i) {
-    if(diag + i < na + nb) {
-      bool take_needle = bi >= nb || (ai < na && needle_first(a_key, b_key));
-      if(take_needle) {
-        found[ai] = b0 + bi;
-        ++ai;
-        if(ai < na) a_key = ka[ai];
-      } else {
-        ++bi;
-        if(bi < nb) b_key = kb[bi];
-      }
-    }
-  }
+  serial_search_merge<vt>(ka, na, kb, nb, lo, diag, b0, found, needle_first);
   __syncthreads();
   for(int i = tid; i < na; i += nt) indices[a0 + i] = found[i];
 }
@@ -265,23 +281,8 @@ sorted_search_stream_k(const type_t* needles, int num_needles,
       if(needle_first(ka[mid], kb[diag - 1 - mid])) lo = mid + 1;
       else hi = mid;
     }
-    int ai = lo, bi = diag - lo;
-    type_t a_key = ai < na ? ka[ai] : type_t();
-    type_t b_key = bi < nb ? kb[bi] : type_t();
-    #pragma unroll
-    for(int i = 0; i < vt; ++i) {
-      if(diag + i < na + nb) {
-        bool take_needle = bi >= nb || (ai < na && needle_first(a_key, b_key));
-        if(take_needle) {
-          found[ai] = w.b0 + bi;
-          ++ai;
-          if(ai < na) a_key = ka[ai];
-        } else {
-          ++bi;
-          if(bi < nb) b_key = kb[bi];
-        }
-      }
-    }
+    serial_search_merge<vt>(ka, na, kb, nb, lo, diag, w.b0, found,
+      needle_first);
     // The keys are no longer needed: the producer may refill the stage while
     // the bounds are being written out.
     ptx::mbar_arrive(&shared.empty[s]);
