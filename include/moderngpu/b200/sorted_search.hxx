@@ -42,10 +42,20 @@ namespace detail {
 // static shared memory of the one-CTA-per-tile kernel).
 typedef search_tuning_t<256, 15> search_default_tuning;
 
-template<typename launch_arg_t>
-struct pick_search_tuning { typedef search_default_tuning type; };
-template<int nt, int vt>
-struct pick_search_tuning<search_tuning_t<nt, vt> > {
+// 4-byte keys take the larger tile (47 KB of static shared memory in the
+// one-CTA-per-tile kernel, just under its limit). Scratch is always sized for
+// the default, smaller tile, which needs the longer partition table.
+template<typename type_t, int size = (int)sizeof(type_t)>
+struct search_tuning_for { typedef search_default_tuning type; };
+template<typename type_t>
+struct search_tuning_for<type_t, 4> { typedef search_tuning_t<256, 23> type; };
+
+template<typename launch_arg_t, typename type_t>
+struct pick_search_tuning {
+  typedef typename search_tuning_for<type_t>::type type;
+};
+template<int nt, int vt, typename type_t>
+struct pick_search_tuning<search_tuning_t<nt, vt>, type_t> {
   typedef search_tuning_t<nt, vt> type;
 };
 
@@ -375,7 +385,9 @@ template<bounds_t bounds, typename launch_arg_t = empty_t,
   typename comp_it>
 void sorted_search(needles_it needles, int num_needles, haystack_it haystack,
   int num_haystack, indices_it indices, comp_it comp, context_t& context) {
-  typedef typename detail::pick_search_tuning<launch_arg_t>::type tuning_t;
+  typedef typename std::iterator_traits<needles_it>::value_type key_t;
+  typedef typename detail::pick_search_tuning<launch_arg_t, key_t>::type
+    tuning_t;
   if(num_needles < 0 || num_haystack < 0 ||
     (int64_t)num_needles + num_haystack > (int64_t)0x7fffffff - 65536)
     throw cuda_exception_t(cudaErrorInvalidValue);

@@ -687,13 +687,14 @@ int mgpu_b200_sorted_search(int dtype, int upper, const void* needles_device,
   cudaStream_t s = (cudaStream_t)stream;
   cudaMemsetAsync(workspace_device, 0, 128, s);
   int* partitions = (int*)((char*)workspace_device + 128);
-  typedef detail::search_default_tuning tuning_t;
   #define MGPU_B200_SEARCH(type_t) \
-    if(upper) detail::sorted_search_enqueue<bounds_upper, tuning_t>( \
+    if(upper) detail::sorted_search_enqueue<bounds_upper, \
+      detail::search_tuning_for<type_t>::type>( \
       (const type_t*)needles_device, num_needles, \
       (const type_t*)haystack_device, num_haystack, indices_device, \
       less_t<type_t>(), partitions, s); \
-    else detail::sorted_search_enqueue<bounds_lower, tuning_t>( \
+    else detail::sorted_search_enqueue<bounds_lower, \
+      detail::search_tuning_for<type_t>::type>( \
       (const type_t*)needles_device, num_needles, \
       (const type_t*)haystack_device, num_haystack, indices_device, \
       less_t<type_t>(), partitions, s);
