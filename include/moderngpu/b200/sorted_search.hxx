@@ -179,13 +179,13 @@ template<bounds_t bounds, typename tuning_t, int stages, typename type_t,
 __global__ void __launch_bounds__(tuning_t::nt + 32)
 sorted_search_stream_k(const type_t* needles, int num_needles,
   const type_t* haystack, int num_haystack, indices_it indices, comp_t comp,
-  const int* partitions, int num_tiles) {
+  const int* partitions, int num_tiles, uint64_t timeout_ns,
+  uint32_t* status) {
   enum { nt = tuning_t::nt, vt = tuning_t::vt, nv = tuning_t::nv,
     warps = nt / 32, per16 = 16 / (int)sizeof(type_t) };
   typedef search_stream_smem_t<tuning_t, stages, type_t> smem_t;
   extern __shared__ __align__(128) char search_raw[];
   smem_t& shared = *reinterpret_cast<smem_t*>(search_raw);
-  const uint64_t timeout_ns = 2000000000ull;
 
   const int tid = (int)threadIdx.x;
   if(0 == tid) {
@@ -232,8 +232,11 @@ sorted_search_stream_k(const type_t* needles, int num_needles,
         q1 = partitions[tile + step + 1];
       }
       if(k >= stages &&
-        !ptx::mbar_wait(&shared.empty[s], ((k / stages) - 1) & 1, timeout_ns))
+        !ptx::mbar_wait(&shared.empty[s], ((k / stages) - 1) & 1, timeout_ns)) {
+        // The stage was never released: give up and say so.
+        if(status) atomicMax(status, (uint32_t)status_copy_timeout);
         return;
+      }
       const long long d0 = (long long)tile * nv;
       const long long d1 = d0 + nv < total ? d0 + nv : total;
       search_window_t w;
@@ -281,7 +284,12 @@ sorted_search_stream_k(const type_t* needles, int num_needles,
     // by plain loads.
     for(int i = w.a_bulk - w.a0 + tid; i < na; i += nt) ka[i] = needles[w.a0 + i];
     for(int i = w.b_bulk - w.b0 + tid; i < nb; i += nt) kb[i] = haystack[w.b0 + i];
-    if(!ptx::named_all<1, nt>(arrived)) return;
+    if(!ptx::named_all<1, nt>(arrived)) {
+      // A staged copy did not complete in time: the remaining bounds stay
+      // unwritten and the status word tells the host.
+      if(0 == tid && status) atomicMax(status, (uint32_t)status_copy_timeout);
+      return;
+    }
 
     int* found = shared.found[k & 1];
     const int diag = min(tid * vt, na + nb);
@@ -314,7 +322,8 @@ template<bounds_t bounds, typename tuning_t, typename needles_it,
   typename haystack_it, typename indices_it, typename comp_t>
 void sorted_search_enqueue(needles_it needles, int num_needles,
   haystack_it haystack, int num_haystack, indices_it indices, comp_t comp,
-  int* partitions, cudaStream_t stream) {
+  int* partitions, cudaStream_t stream,
+  uint64_t timeout_ns = 2000000000ull, uint32_t* status = nullptr) {
   typedef typename std::iterator_traits<needles_it>::value_type type_t;
   if(!num_needles) return;
   int num_tiles = (int)div_up((int64_t)num_needles + num_haystack,
@@ -355,7 +364,7 @@ void sorted_search_enqueue(needles_it needles, int num_needles,
       if(grid > num_tiles) grid = num_tiles;
       kernel<<<grid, threads, smem, stream>>>((const type_t*)needles,
         num_needles, (const type_t*)haystack, num_haystack, indices, comp,
-        partitions, num_tiles);
+        partitions, num_tiles, timeout_ns, status);
       return;
     }
   }

@@ -219,6 +219,9 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
     uint64_t start = 0;
     for(uint32_t spin = 0; ; ++spin) {
       code = state.peek(base, value);
+      // Lane 0's view decides for the whole warp, so that every lane leaves
+      // the loop in the same iteration and the shuffles below stay converged.
+      code = __shfl_sync(full, code, 0);
       if(tile_empty != code) break;
       if(spin > 16) __nanosleep(100);
       if(31 == (spin & 31)) {
@@ -227,7 +230,6 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
         else if(now - start > timeout_ns) break;
       }
     }
-    code = __shfl_sync(full, code, 0);
     value = shfl_any(value, 0);
     if(tile_empty == code) {
       if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);

@@ -85,9 +85,13 @@ int mgpu_b200_segreduce(int dtype, int op, const void* input_device, int count,
  * part of the loaded library, so every GPU that loads the library holds it
  * until the process exits. The call allocates and frees nothing.
  *  - A problem whose scratch exceeds the block is refused with
- *    MGPU_B200_E_WORKSPACE before anything is launched (4-byte types fit up
- *    to the library's overall size limit; 8-byte types up to roughly 4e8
- *    items + segments).
+ *    MGPU_B200_E_WORKSPACE before anything is launched. The scratch is about
+ *    132 bytes per tile (one 128-byte status line + one partition entry), so
+ *    the block serves 31,773 tiles: count + num_segments up to 227,494,680
+ *    for 4-byte types (tiles of 7,160) and 211,226,904 for 8-byte types
+ *    (tiles of 6,648). 2^27 items with 2^22 segments fit; 2^28 items do not.
+ *    mgpu_b200_segreduce_workspace_bytes(dtype, count, num_segments) <=
+ *    mgpu_b200_static_scratch_bytes() is the exact test.
  *  - All calls on one GPU share the block, which keeps the previous call's
  *    contents; the kernels clear what must start at zero. Calls that overlap
  *    on a GPU (two streams, two host threads) race on it: run them one after

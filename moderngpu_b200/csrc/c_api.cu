@@ -175,11 +175,16 @@ int expand_typed(const void* input, int count, const int* segments,
   int num_segments, void* output, void* workspace, cudaStream_t stream) {
   uint32_t* status = (uint32_t*)workspace + 1;
   int* partitions = (int*)((char*)workspace + 128);
-  cudaMemsetAsync(workspace, 0, 128, stream);
-  detail::transform_lbs_enqueue<lbs_tuning>(
-    expand_t<elem_t> { (elem_t*)output }, count, segments, num_segments,
-    make_tuple((const elem_t*)input), partitions, stream, g_timeout_ns,
-    status);
+  cudaError_t cleared = cudaMemsetAsync(workspace, 0, 128, stream);
+  if(cudaSuccess != cleared) return cuda_code(cleared);
+  try {
+    detail::transform_lbs_enqueue<lbs_tuning>(
+      expand_t<elem_t> { (elem_t*)output }, count, segments, num_segments,
+      make_tuple((const elem_t*)input), partitions, stream, g_timeout_ns,
+      status);
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
+  }
   return last_launch_code();
 }
 
@@ -617,11 +622,16 @@ int mgpu_b200_load_balance_search(int count, const int* segments_device,
   cudaStream_t s = (cudaStream_t)stream;
   uint32_t* status = (uint32_t*)workspace_device + 1;
   int* partitions = (int*)((char*)workspace_device + 128);
-  cudaMemsetAsync(workspace_device, 0, 128, s);
-  detail::transform_lbs_enqueue<lbs_tuning>(
-    store_seg_rank_t { seg_out_device, rank_out_device }, count,
-    segments_device, num_segments, tuple<>(), partitions, s, g_timeout_ns,
-    status);
+  cudaError_t cleared = cudaMemsetAsync(workspace_device, 0, 128, s);
+  if(cudaSuccess != cleared) return cuda_code(cleared);
+  try {
+    detail::transform_lbs_enqueue<lbs_tuning>(
+      store_seg_rank_t { seg_out_device, rank_out_device }, count,
+      segments_device, num_segments, tuple<>(), partitions, s, g_timeout_ns,
+      status);
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
+  }
   return last_launch_code();
 }
 
@@ -685,25 +695,31 @@ int mgpu_b200_sorted_search(int dtype, int upper, const void* needles_device,
     return MGPU_B200_E_WORKSPACE;
   if((uintptr_t)workspace_device % 128) return MGPU_B200_E_INVALID;
   cudaStream_t s = (cudaStream_t)stream;
-  cudaMemsetAsync(workspace_device, 0, 128, s);
+  cudaError_t cleared = cudaMemsetAsync(workspace_device, 0, 128, s);
+  if(cudaSuccess != cleared) return cuda_code(cleared);
+  uint32_t* status = (uint32_t*)workspace_device + 1;
   int* partitions = (int*)((char*)workspace_device + 128);
   #define MGPU_B200_SEARCH(type_t) \
     if(upper) detail::sorted_search_enqueue<bounds_upper, \
       detail::search_tuning_for<type_t>::type>( \
       (const type_t*)needles_device, num_needles, \
       (const type_t*)haystack_device, num_haystack, indices_device, \
-      less_t<type_t>(), partitions, s); \
+      less_t<type_t>(), partitions, s, g_timeout_ns, status); \
     else detail::sorted_search_enqueue<bounds_lower, \
       detail::search_tuning_for<type_t>::type>( \
       (const type_t*)needles_device, num_needles, \
       (const type_t*)haystack_device, num_haystack, indices_device, \
-      less_t<type_t>(), partitions, s);
-  switch(dtype) {
-    case MGPU_B200_I32: MGPU_B200_SEARCH(int) break;
-    case MGPU_B200_I64: MGPU_B200_SEARCH(long long) break;
-    case MGPU_B200_F32: MGPU_B200_SEARCH(float) break;
-    case MGPU_B200_F64: MGPU_B200_SEARCH(double) break;
-    default: return MGPU_B200_E_UNSUPPORTED;
+      less_t<type_t>(), partitions, s, g_timeout_ns, status);
+  try {
+    switch(dtype) {
+      case MGPU_B200_I32: MGPU_B200_SEARCH(int) break;
+      case MGPU_B200_I64: MGPU_B200_SEARCH(long long) break;
+      case MGPU_B200_F32: MGPU_B200_SEARCH(float) break;
+      case MGPU_B200_F64: MGPU_B200_SEARCH(double) break;
+      default: return MGPU_B200_E_UNSUPPORTED;
+    }
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
   }
   #undef MGPU_B200_SEARCH
   return last_launch_code();

@@ -78,8 +78,9 @@ def segreduce(values, segments, op="plus", init=0, threads=1):
     return out
 
 
-def segsum_wide(values, segments, init=0.0):
-    """Plus-reduction accumulated in a wider type; returns (sums, magnitudes)."""
+def segsum_wide(values, segments, init=0.0, threads=1):
+    """Plus-reduction accumulated in a wider type; returns (sums, magnitudes).
+    threads > 1 spreads the segments over OpenMP threads."""
     values = np.ascontiguousarray(values)
     seg = _seg(segments)
     sums = np.empty(seg.size, dtype=np.float64)
@@ -87,8 +88,22 @@ def segsum_wide(values, segments, init=0.0):
     fn = {np.dtype(np.float32): lib().oracle_segsum_f32_wide,
           np.dtype(np.float64): lib().oracle_segsum_f64_wide}[values.dtype]
     fn(_ptr(values), ctypes.c_int64(values.size), _ptr(seg),
-       ctypes.c_int(seg.size), _ptr(sums), _ptr(mags), ctypes.c_double(init))
+       ctypes.c_int(seg.size), _ptr(sums), _ptr(mags), ctypes.c_double(init),
+       ctypes.c_int(threads))
     return sums, mags
+
+
+def place_by_segments(values, segments, threads):
+    """A copy of the float32 array `values` whose pages were first touched by
+    the OpenMP threads that segreduce(..., threads=threads) will read them
+    with (timing aid of the CPU baseline)."""
+    values = np.ascontiguousarray(values, dtype=np.float32)
+    seg = _seg(segments)
+    placed = np.empty_like(values)
+    lib().oracle_place_by_segments_f32(_ptr(values), ctypes.c_int64(values.size),
+                                       _ptr(seg), ctypes.c_int(seg.size),
+                                       _ptr(placed), ctypes.c_int(threads))
+    return placed
 
 
 def segreduce_index_mod(count, segments, init=-1, modulus=13):

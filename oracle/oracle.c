@@ -85,7 +85,9 @@ DEFINE_SEGREDUCE(oracle_segreduce_f64, double)
  */
 void oracle_segsum_f32_wide(const float* input, int64_t count,
   const int32_t* segments, int num_segments, double* sums, double* magnitudes,
-  double init) {
+  double init, int threads) {
+  (void)threads;
+  #pragma omp parallel for schedule(static, 4096) num_threads(threads) if(threads > 1)
   for(int s = 0; s < num_segments; ++s) {
     int64_t begin = segments[s];
     int64_t end = seg_end(segments, num_segments, count, s);
@@ -101,7 +103,9 @@ void oracle_segsum_f32_wide(const float* input, int64_t count,
 
 void oracle_segsum_f64_wide(const double* input, int64_t count,
   const int32_t* segments, int num_segments, double* sums, double* magnitudes,
-  double init) {
+  double init, int threads) {
+  (void)threads;
+  #pragma omp parallel for schedule(static, 4096) num_threads(threads) if(threads > 1)
   for(int s = 0; s < num_segments; ++s) {
     int64_t begin = segments[s];
     int64_t end = seg_end(segments, num_segments, count, s);
@@ -112,6 +116,24 @@ void oracle_segsum_f64_wide(const double* input, int64_t count,
     }
     sums[s] = (end > begin) ? (double)acc : init;
     magnitudes[s] = (double)mag;
+  }
+}
+
+/*
+ * Copies `input` into `placed` with the loop and schedule of the segreduce
+ * above, so that every page of a freshly allocated `placed` is first touched
+ * by the thread that will later reduce it (memory placement on hosts with
+ * several NUMA nodes). Timing aid of the CPU baseline; computes nothing.
+ */
+void oracle_place_by_segments_f32(const float* input, int64_t count,
+  const int32_t* segments, int num_segments, float* placed, int threads) {
+  (void)threads;
+  #pragma omp parallel for schedule(static, 4096) num_threads(threads) if(threads > 1)
+  for(int s = 0; s < num_segments; ++s) {
+    int64_t begin = s ? segments[s] : 0;
+    int64_t end = seg_end(segments, num_segments, count, s);
+    if(end > begin)
+      memcpy(placed + begin, input + begin, (size_t)(end - begin) * sizeof(float));
   }
 }
 

@@ -169,6 +169,22 @@ int ref_lbs_segreduce_seg_plus_rank(int count, const int* segments,
   return finish();
 }
 
+// lbs_segreduce with a per-segment cached weight
+// (src/moderngpu/kernel_segreduce.hxx:303-387):
+// f(index, seg, rank, tuple<weight>) = values[index] * weight, op plus, init 0.
+int ref_lbs_segreduce_weighted_f32(const float* values, int count,
+  const int* segments, int num_segments, const float* weights, float* output,
+  int pooled, int sync) {
+  try {
+    lbs_segreduce([=]MGPU_DEVICE(int index, int seg, int rank,
+      tuple<float> weight) {
+      return values[index] * get<0>(weight);
+    }, count, segments, num_segments, make_tuple(weights), output,
+      plus_t<float>(), 0.0f, pick(pooled));
+  } catch(cuda_exception_t& e) { return (int)e.result; }
+  return sync ? finish() : 0;
+}
+
 // Host-vector round trip through the reference's API: to_mem, segreduce,
 // from_mem (src/moderngpu/memory.hxx:61-75), fp32 plus.
 int ref_segreduce_f32_host(const float* input_host, int count,

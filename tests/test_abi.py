@@ -70,6 +70,34 @@ def test_invalid_arguments_are_rejected_before_any_launch(mgpu):
                                                  None) == E_INVALID
 
 
+def test_static_scratch_capacity_matches_the_header(mgpu):
+    """The limits include/moderngpu_b200.h states for
+    mgpu_b200_segreduce_static: the block is 4 MiB, 2^27 items fit, 2^28 do
+    not, and the largest sizes that fit are the ones written there. Host-side
+    arithmetic only (sizes are checked before any pointer is used)."""
+    lib = mgpu.load_library()
+    lib.mgpu_b200_static_scratch_bytes.restype = ctypes.c_size_t
+    cap = lib.mgpu_b200_static_scratch_bytes()
+    assert cap == 4 << 20
+    need = lib.mgpu_b200_segreduce_workspace_bytes
+    assert need(0, 1 << 27, 1 << 22) <= cap
+    assert need(0, 1 << 28, 1 << 23) > cap
+    header = open(HEADER).read()
+    for dtype, limit in ((0, 227_494_680), (2, 227_494_680),
+                         (1, 211_226_904), (3, 211_226_904)):
+        assert need(dtype, limit, 0) <= cap < need(dtype, limit + 1, 0)
+        assert "{:,}".format(limit) in header
+    init = ctypes.c_float(0)
+    E_WORKSPACE = 2
+    # One element beyond the limit is refused before any pointer is touched.
+    assert lib.mgpu_b200_segreduce_static(
+        0, 0, None, 227_494_681, None, 0, None, ctypes.byref(init),
+        None) == E_WORKSPACE
+    assert lib.mgpu_b200_segreduce_static(
+        1, 0, None, 211_226_000, None, 905, None, ctypes.byref(init),
+        None) == E_WORKSPACE
+
+
 def test_missing_library_fails_loudly(monkeypatch):
     import moderngpu_b200.binding as binding
     monkeypatch.setattr(binding, "_lib", None)

@@ -155,21 +155,19 @@ def test_dropin_load_balance_program():
 
 
 def test_dropin_segreduce_program():
-    """tests/test_segreduce.cu, unmodified, built on this repo's headers. It
-    loops over 1000 seeds of 1e8 items with a serial host check, so it is cut
-    off after a while; every seed finished by then must have passed."""
+    """tests/test_segreduce.cu, unmodified, built on this repo's headers. The
+    file's own main() loops over 1000 seeds of 1e8 items with a serial host
+    check; the build renames it away and a small driver calls the file's test
+    function for three seeds, so the program ends by itself."""
     exe = os.path.join(REF_DIR, "dropin_test_segreduce")
     if not os.path.exists(exe):
         pytest.skip("drop-in test binary not built")
-    try:
-        run = subprocess.run(["stdbuf", "-oL", exe], capture_output=True,
-                             text=True, timeout=25)
-        out = run.stdout
-    except subprocess.TimeoutExpired as e:
-        out = (e.stdout or b"").decode() if isinstance(e.stdout, bytes) \
-            else (e.stdout or "")
-    assert "Reduction error" not in out
-    assert out.count("passed") >= 2
+    run = subprocess.run([exe, "3"], capture_output=True, text=True,
+                         timeout=600)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "Reduction error" not in run.stdout
+    assert run.stdout.count("passed") == 3
+    assert "finished 3 seeds" in run.stdout
 
 
 def test_template_program_on_the_reference_itself():

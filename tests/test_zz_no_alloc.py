@@ -74,3 +74,35 @@ def test_too_large_for_the_block_is_refused_without_launching(mgpu):
     code = lib.mgpu_b200_segreduce_static(0, 0, None, 2**31 - 1, None, 2**20,
                                           None, ctypes.byref(init), None)
     assert code == 2
+
+
+def test_largest_problem_that_fits_runs_and_the_next_tile_is_refused(mgpu):
+    """At the boundary the header documents: 227,494,680 fp32 items + segments
+    use the whole 4 MiB block and reduce correctly; one more element needs
+    another tile and is refused."""
+    lib = mgpu.load_library()
+    limit = 227_494_680
+    num_segments = 1 << 20
+    count = limit - num_segments
+    assert lib.mgpu_b200_segreduce_workspace_bytes(0, count, num_segments) \
+        == 4 << 20
+    g = torch.Generator(device="cuda").manual_seed(3)
+    values = torch.randint(-8, 9, (count,), device="cuda", generator=g,
+                           dtype=torch.int32).to(torch.float32)
+    seg = (torch.arange(num_segments, device="cuda", dtype=torch.int64)
+           * (count // num_segments)).to(torch.int32)
+    got = mgpu.segreduce_static(values, seg, op="plus", init=0.0)
+    want = mgpu.segreduce(values, seg, op="plus", init=0.0)
+    torch.cuda.synchronize()
+    # Small integers in fp32: every order of summation gives the same bits.
+    assert torch.equal(got, want)
+    sums = torch.zeros(num_segments, dtype=torch.float64, device="cuda")
+    ids = torch.clamp(torch.arange(count, device="cuda") //
+                      (count // num_segments), max=num_segments - 1)
+    sums.index_add_(0, ids, values.double())
+    assert torch.equal(got.double(), sums)
+    init = ctypes.c_float(0)
+    code = lib.mgpu_b200_segreduce_static(
+        0, 0, values.data_ptr(), count + 1, seg.data_ptr(), num_segments,
+        got.data_ptr(), ctypes.byref(init), None)
+    assert code == 2                          # MGPU_B200_E_WORKSPACE
