@@ -85,7 +85,7 @@ class ClockSampler:
 
     def __init__(self, uuid, index):
         self.uuid, self.index = uuid, index
-        self.samples = []          # (time, sm_mhz, reasons_mask)
+        self.samples = []          # (time, sm_mhz, reasons_mask, mem_mhz)
         self.max_mhz = None
         self.stop_flag = threading.Event()
         self.thread = None
@@ -109,8 +109,10 @@ class ClockSampler:
                             handle, pynvml.NVML_CLOCK_SM)
                         mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(
                             handle)
+                        mem = pynvml.nvmlDeviceGetClockInfo(
+                            handle, pynvml.NVML_CLOCK_MEM)
                         self.samples.append((time.perf_counter(), float(mhz),
-                                             int(mask)))
+                                             int(mask), float(mem)))
                     except Exception:
                         pass
                     time.sleep(0.004)
@@ -139,8 +141,10 @@ class ClockSampler:
         for s in inside:
             mask |= s[2]
         mhz = sorted(s[1] for s in inside)
+        mem = sorted(s[3] for s in inside)
         return {"sm_mhz": statistics.median(mhz) if mhz else None,
                 "sm_max_mhz": self.max_mhz,
+                "mem_mhz": statistics.median(mem) if mem else None,
                 "reasons": sorted(k for k, bit in self.REASONS.items()
                                   if mask & bit),
                 "samples": len(inside), "note": note}

@@ -237,7 +237,12 @@ struct segreduce_smem_t {
     // spmv stages one int32 column index per item on top of everything else.
     // lbs_segreduce keeps one int32 segment id per item there instead.
     cols_bytes = (2 == source_kind || 3 == source_kind) ? nv * 4 + 48 : 0,
-    stage_bytes = (nv * wide + 8 * elem + 64 + cols_bytes + 127) / 128 * 128,
+    // Slots in front of the values that shifted run ends may use (see the
+    // fold): nt - 1 of them, arithmetic types only.
+    pad_bytes = std::is_arithmetic<type_t>::value ?
+      (nt * elem + 127) / 128 * 128 : 0,
+    stage_bytes = pad_bytes +
+      (nv * wide + 8 * elem + 64 + cols_bytes + 127) / 128 * 128,
     ring = 32
   };
   struct fixed_t {
@@ -286,7 +291,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   enum { nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
     nv = tuning_t::nv, warps = nt / 32, flag_words = layout_t::flag_words,
     elem = layout_t::elem, stage_bytes = layout_t::stage_bytes,
-    ring = layout_t::ring,
+    pad_bytes = layout_t::pad_bytes, ring = layout_t::ring,
     src_bulk = source_t::bulk,
     seg_bulk = segments_are_int_array<segments_it>::value };
 
@@ -372,7 +377,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       d.b0 = (int)b0;
       d.b1 = (int)b1;
       d.pad = 0;
-      char* stage = stage_base + s * stage_bytes;
+      char* stage = stage_base + s * stage_bytes + pad_bytes;
       int na = d.a1 - d.a0;
 
       // Item window: whole 16-byte granules of the input array.
@@ -560,15 +565,20 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   const unsigned full_mask = 0xffffffffu;
   const uint32_t vt_mask = (1u << vt) - 1;
   const int edge_thread_a = nt / 2, edge_thread_b = nt / 2 + 32;
-  int tiles_done = 0;
-  for(int it = 0; ; ++it) {
+  // One tile. The body exists in two forms, chosen once per CTA (below): the
+  // plain one keeps every run end in place; the shifting one (staged arrays
+  // of arithmetic values only) takes the values into registers early and
+  // keeps run ends in shifted slots. Returns false when there are no more
+  // tiles.
+  auto consume_tile = [&](auto shifting_tag, const int it) -> bool {
+    constexpr bool shifting = decltype(shifting_tag)::value;
     int s = it % stages;
     if(!ptx::mbar_wait(&fixed.full[s], (it / stages) & 1, args.timeout_ns))
       atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
     const tile_desc_t d = fixed.desc[s];
-    if(d.tile < 0) break;
+    if(d.tile < 0) return false;
 
-    char* stage = stage_base + s * stage_bytes;
+    char* stage = stage_base + s * stage_bytes + pad_bytes;
     type_t* vals = reinterpret_cast<type_t*>(stage);
     int* offs = reinterpret_cast<int*>(stage + d.offs_byte);
     uint32_t* flags = fixed.flags[it & 1];
@@ -684,7 +694,38 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       atomicOr(&flags[hi >> 5], 1u << (hi & 31));
       if(lo) atomicOr(&flags[lo >> 5], 1u << (lo & 31));
     }
+    // The thread's range of positions, [w0 + i_lo, w0 + i_hi) of
+    // [w0, w0 + vt), and whether the unrolled fold serves it. For arithmetic
+    // types that path also serves the threads that straddle the tile's
+    // edges: padding positions hold arbitrary bits whose folds are never
+    // stored or propagated, thanks to the sentinels.
+    const int w0 = tid * vt;
+    const int i_lo = lo > w0 ? lo - w0 : 0;
+    const int i_hi = hi - w0 < vt ? hi - w0 : vt;
+    const bool inside = w0 + i_lo >= src_lo && w0 + i_hi <= src_hi;
+    const bool fast = std::is_arithmetic<type_t>::value ?
+      (i_lo < i_hi && inside) : (inside && 0 == i_lo && vt == i_hi);
+    // The shifting form takes the values into registers BEFORE the barrier:
+    // after it no thread of a fully staged tile still needs its range of the
+    // stage, so a run end may be stored anywhere in it (see below).
+    enum { early_load = shifting };
+    type_t v[vt];
+    if constexpr (early_load) { if(fast) load_chunk<vt>(vals + w0, v); }
     ptx::named_sync<1, nt>();
+    // The shifting form of the body: in a tile that is whole in its stage the
+    // run end at position e, which thread e / vt produces, is kept
+    // nt - 1 - e / vt slots to the left of e. The shift shrinks from thread to
+    // thread, so no two run ends share a slot; it spreads ends that are a
+    // multiple of 8 apart over all banks; and since it is constant within a
+    // thread the fold's stores keep their immediate offsets. Slots lie in
+    // other threads' ranges (or in the pad in front of the values): every
+    // thread took its values into registers before the barrier above.
+    const bool shifted = early_load && all_staged && src_lo <= lo &&
+      src_hi >= hi;
+    const int my_shift = shifted ? nt - 1 - tid : 0;
+    auto slot_of = [&](int e) -> int {
+      return shifted ? e - (nt - 1 - e / vt) : e;
+    };
 
     if constexpr (3 == src_bulk) {
       // Segment of every item (running maximum of head ids: thread, warp,
@@ -753,32 +794,24 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
 
     if(na > 0) {
       // 2. Per-thread fold of positions [w0, w0 + vt). The value of every
-      // run that ends inside the thread's range is stored in place; the
-      // first of them still lacks what precedes the thread (step 4).
-      // For arithmetic types the unrolled path also serves the threads that
-      // straddle the tile's edges: padding positions hold arbitrary bits
-      // whose folds are never stored or propagated, thanks to the sentinels.
-      const int w0 = tid * vt;
-      int i_lo = lo > w0 ? lo - w0 : 0;
-      int i_hi = hi - w0 < vt ? hi - w0 : vt;
-      const bool inside = w0 + i_lo >= src_lo && w0 + i_hi <= src_hi;
-      const bool fast = std::is_arithmetic<type_t>::value ?
-        (i_lo < i_hi && inside) : (inside && 0 == i_lo && vt == i_hi);
+      // run that ends inside the thread's range is stored in place (shifted
+      // tiles: in its shifted slot); the first of them still lacks what
+      // precedes the thread (step 4).
       uint32_t bits = __funnelshift_r(flags[w0 >> 5], flags[(w0 >> 5) + 1],
         w0 & 31);
       uint32_t ends = bits >> 1;
 
       type_t x = init;
       bool head = true;
+      type_t* own = vals + w0 - my_shift;   // where this thread's run ends go
       if(fast) {
-        type_t v[vt];
-        load_chunk<vt>(vals + w0, v);
+        if constexpr (!early_load) load_chunk<vt>(vals + w0, v);
         x = v[0];
-        if(ends & 1) vals[w0] = x;
+        if(ends & 1) own[0] = x;
         #pragma unroll
         for(int i = 1; i < vt; ++i) {
           x = ((bits >> i) & 1) ? v[i] : op(x, v[i]);
-          if((ends >> i) & 1) vals[w0 + i] = x;
+          if((ends >> i) & 1) own[i] = x;
         }
         head = 0 != (bits & vt_mask);
         ends &= vt_mask;
@@ -837,8 +870,8 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           has_c = true;
         }
         if(has_c) {
-          int e1 = w0 + __ffs(ends) - 1;
-          vals[e1] = op(c, vals[e1]);
+          int e1 = __ffs(ends) - 1;
+          own[e1] = op(c, own[e1]);
         }
       }
     }
@@ -868,7 +901,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           p0 = all_staged ? seg_start_staged(b0) : seg_start(b0);
           unsigned q0 = (unsigned)(p0 - a0);
           if(q0 > (unsigned)na) q0 = p0 < a0 ? 0u : (unsigned)na;
-          if(q0 > 0) lead = vals[lo + (int)q0 - 1];
+          if(q0 > 0) lead = vals[slot_of(lo + (int)q0 - 1)];
         }
         e.tile = d.tile; e.a0 = a0; e.na = na; e.b0 = b0; e.nb = nb;
         e.has_first = has_first; e.prev0 = prev0; e.p0 = p0;
@@ -877,7 +910,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       }
       if(edge_thread_b == tid) {
         type_t tail = init;
-        if(na > 0) tail = vals[hi - 1];
+        if(na > 0) tail = vals[slot_of(hi - 1)];
         int p_last = a1 - 1;
         if(nb > 0)
           p_last = all_staged ? seg_start_staged(b1 - 1) : seg_start(b1 - 1);
@@ -897,7 +930,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       unsigned rel = (unsigned)(p - a0);
       if(rel > (unsigned)na) rel = (unsigned)na;
       if(rel < 1u) rel = 1u;
-      value = vals[lo + (int)rel - 1];
+      value = vals[slot_of(lo + (int)rel - 1)];
       return true;
     };
     {
@@ -916,7 +949,37 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       ptx::mbar_arrive(&fixed.empty[s]);
       if(write) args.output[j - 1] = value;
     }
-    ++tiles_done;
+    return true;
+  };
+
+  // Rows of one fixed width whose length is a multiple of 8 (the usual shape
+  // of a dense-ish matrix or a batched reduction) put every run end of a tile
+  // into one or two shared-memory banks when the ends are kept in place: a
+  // third more time on rows of 16 or 32 fp32 items. The shifting form has no
+  // such shape but costs ~2 % elsewhere, so a CTA picks by looking at the
+  // segment starts of its first tile: all at the same position modulo 8 (and
+  // at least 64 of them) means fixed-width rows.
+  int tiles_done = 0;
+  bool shifting = false;
+  if constexpr (1 == src_bulk && seg_bulk && std::is_arithmetic<type_t>::value) {
+    if(!ptx::mbar_wait(&fixed.full[0], 0, args.timeout_ns))
+      atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+    const tile_desc_t d = fixed.desc[0];
+    bool aligned = d.tile >= 0 && d.b1 - d.b0 >= 64;
+    if(aligned) {
+      const int* offs = reinterpret_cast<const int*>(
+        stage_base + pad_bytes + d.offs_byte);
+      // Staged starts of segments [ob, oe); compare those of the tile.
+      int j = d.b0 + tid, j0 = d.b0;
+      if(j < d.b1 && j >= d.ob && j < d.oe && j0 >= d.ob)
+        aligned = 0 == ((offs[j - d.ob] ^ offs[j0 - d.ob]) & 7);
+    }
+    shifting = ptx::named_all<1, nt>(aligned);
+  }
+  if(shifting) {
+    while(consume_tile(std::true_type(), tiles_done)) ++tiles_done;
+  } else {
+    while(consume_tile(std::false_type(), tiles_done)) ++tiles_done;
   }
   if(edge_thread_a == tid || edge_thread_b == tid) {
     // One end-of-work record for each carry warp.

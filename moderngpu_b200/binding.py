@@ -11,7 +11,10 @@ import os
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-_LIB_PATH = os.path.join(_PKG_DIR, "lib", "libmgpu_b200.so")
+# MGPU_B200_LIBRARY names another build of the library to load instead of the
+# in-tree one (comparing two builds on one machine).
+_LIB_PATH = os.environ.get("MGPU_B200_LIBRARY") or os.path.join(
+    _PKG_DIR, "lib", "libmgpu_b200.so")
 
 F32, F64, I32, I64 = 0, 1, 2, 3
 PLUS, MAX, MIN = 0, 1, 2
@@ -443,19 +446,28 @@ def spmv(matrix, columns, vector, row_starts, out=None, workspace=None):
     return out
 
 
-def transform_lbs(count, segments, want_ranks=True, workspace=None):
+def transform_lbs(count, segments, want_ranks=True, workspace=None,
+                  out_seg=None, out_rank=None):
     """mgpu::transform_lbs with the functor that records (seg, rank) per item.
 
     Returns (seg, rank) int32 tensors of `count` elements (rank is None when
-    want_ranks is False, which is mgpu::load_balance_search).
+    want_ranks is False, which is mgpu::load_balance_search). out_seg and
+    out_rank, when given, receive the results.
     """
     lib = load_library()
     _require_cuda(segments, "segments", torch.int32)
     num_segments = segments.numel()
     dev = segments.device
-    seg = torch.empty(count, dtype=torch.int32, device=dev)
-    rank = torch.empty(count, dtype=torch.int32, device=dev) \
-        if want_ranks else None
+    if out_seg is None:
+        out_seg = torch.empty(count, dtype=torch.int32, device=dev)
+    if want_ranks and out_rank is None:
+        out_rank = torch.empty(count, dtype=torch.int32, device=dev)
+    for name, t in (("out_seg", out_seg), ("out_rank", out_rank)):
+        if t is not None:
+            _require_cuda(t, name, torch.int32)
+            if t.numel() != count:
+                raise ValueError("%s must have one element per item" % name)
+    seg, rank = out_seg, (out_rank if want_ranks else None)
     need = lib.mgpu_b200_lbs_workspace_bytes(count, num_segments)
     if workspace is None:
         workspace = _workspace(dev, need)

@@ -150,15 +150,6 @@ int weighted_typed(const void* values, int count, const int* segments,
 ////////////////////////////////////////////////////////////////////////////////
 // Load-balancing search functors.
 
-struct store_seg_rank_t {
-  int* seg_out;
-  int* rank_out;
-  MGPU_DEVICE void operator()(int index, int seg, int rank, tuple<>) const {
-    seg_out[index] = seg;
-    if(rank_out) rank_out[index] = rank;
-  }
-};
-
 template<typename elem_t>
 struct expand_t {
   elem_t* output;
@@ -169,6 +160,26 @@ struct expand_t {
 };
 
 typedef detail::lbs_default_tuning lbs_tuning;
+typedef detail::lbs_fill_default_tuning fill_tuning;
+
+// 4- and 8-byte elements go through the fill kernel (tile output by bulk
+// copy), 1- and 2-byte elements through the generic functor path.
+template<typename elem_t>
+int expand_fill(const void* input, int count, const int* segments,
+  int num_segments, void* output, void* workspace, cudaStream_t stream) {
+  // The header (ticket counter, status word) is cleared by the partitioner.
+  int* partitions = (int*)((char*)workspace + 128);
+  detail::lbs_fill_args_t<detail::lbs_fill_values, elem_t> out = { };
+  out.values = (const elem_t*)input;
+  out.expanded = (elem_t*)output;
+  try {
+    detail::lbs_fill_enqueue<fill_tuning>(out, count, segments, num_segments,
+      (uint32_t*)workspace, partitions, stream, g_timeout_ns);
+  } catch(cuda_exception_t& e) {
+    return cuda_code(e.result);
+  }
+  return last_launch_code();
+}
 
 template<typename elem_t>
 int expand_typed(const void* input, int count, const int* segments,
@@ -189,8 +200,11 @@ int expand_typed(const void* input, int count, const int* segments,
 }
 
 inline size_t lbs_bytes(int count, int num_segments) {
-  return 128 + (detail::lbs_partition_bytes(count, num_segments,
-    lbs_tuning::nv) + 127) / 128 * 128;
+  // Serves the generic tiles and the (slightly smaller) fill tiles.
+  enum { nv = (int)fill_tuning::nv < (int)lbs_tuning::nv ?
+    (int)fill_tuning::nv : (int)lbs_tuning::nv };
+  return 128 + (detail::lbs_partition_bytes(count, num_segments, nv) + 127) /
+    128 * 128;
 }
 
 ////////////////////////////////////////////////////////////////////////////////
@@ -620,15 +634,22 @@ int mgpu_b200_load_balance_search(int count, const int* segments_device,
   if(workspace_bytes < lbs_bytes(count, num_segments))
     return MGPU_B200_E_WORKSPACE;
   cudaStream_t s = (cudaStream_t)stream;
-  uint32_t* status = (uint32_t*)workspace_device + 1;
+  // The header (ticket counter, status word) is cleared by the partitioner.
+  uint32_t* header = (uint32_t*)workspace_device;
   int* partitions = (int*)((char*)workspace_device + 128);
-  cudaError_t cleared = cudaMemsetAsync(workspace_device, 0, 128, s);
-  if(cudaSuccess != cleared) return cuda_code(cleared);
   try {
-    detail::transform_lbs_enqueue<lbs_tuning>(
-      store_seg_rank_t { seg_out_device, rank_out_device }, count,
-      segments_device, num_segments, tuple<>(), partitions, s, g_timeout_ns,
-      status);
+    if(rank_out_device) {
+      detail::lbs_fill_args_t<detail::lbs_fill_ids_ranks, int> out = { };
+      out.ids = seg_out_device;
+      out.ranks = rank_out_device;
+      detail::lbs_fill_enqueue<fill_tuning>(out, count, segments_device,
+        num_segments, header, partitions, s, g_timeout_ns);
+    } else {
+      detail::lbs_fill_args_t<detail::lbs_fill_ids, int> out = { };
+      out.ids = seg_out_device;
+      detail::lbs_fill_enqueue<fill_tuning>(out, count, segments_device,
+        num_segments, header, partitions, s, g_timeout_ns);
+    }
   } catch(cuda_exception_t& e) {
     return cuda_code(e.result);
   }
@@ -653,9 +674,9 @@ int mgpu_b200_interval_expand(int elem_bytes, const void* input_device,
       num_segments, output_device, workspace_device, s);
     case 2: return expand_typed<uint16_t>(input_device, count, segments_device,
       num_segments, output_device, workspace_device, s);
-    case 4: return expand_typed<uint32_t>(input_device, count, segments_device,
+    case 4: return expand_fill<uint32_t>(input_device, count, segments_device,
       num_segments, output_device, workspace_device, s);
-    case 8: return expand_typed<uint64_t>(input_device, count, segments_device,
+    case 8: return expand_fill<uint64_t>(input_device, count, segments_device,
       num_segments, output_device, workspace_device, s);
   }
   return MGPU_B200_E_UNSUPPORTED;

@@ -79,6 +79,55 @@ def test_unaligned_segments_pointer(mgpu, oracle):
     assert np.array_equal(got_rank.cpu().numpy(), want_rank)
 
 
+@pytest.mark.parametrize("seg_shift,rank_shift", [(0, 0), (1, 1), (2, 3),
+                                                  (3, 0), (0, 2)])
+def test_outputs_at_every_alignment(mgpu, oracle, seg_shift, rank_shift):
+    """A tile's ids and ranks leave shared memory by bulk copies of whole
+    16-byte granules of the output arrays: the arrays may start anywhere in a
+    granule, and the two arrays need not start at the same place in theirs."""
+    rng = np.random.default_rng(seg_shift * 4 + rank_shift)
+    count, num_segments = 777_777, 9001
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    want_seg, want_rank = oracle.load_balance_search(count, seg)
+    guard = -12345
+    seg_buf = torch.full((count + 8,), guard, dtype=torch.int32, device="cuda")
+    rank_buf = torch.full((count + 8,), guard, dtype=torch.int32, device="cuda")
+    mgpu.transform_lbs(count, dev(seg),
+                       out_seg=seg_buf[seg_shift:seg_shift + count],
+                       out_rank=rank_buf[rank_shift:rank_shift + count])
+    assert mgpu.workspace_status() == 0
+    for buf, shift, want in ((seg_buf, seg_shift, want_seg),
+                             (rank_buf, rank_shift, want_rank)):
+        got = buf.cpu().numpy()
+        assert np.array_equal(got[shift:shift + count], want)
+        assert np.all(got[:shift] == guard) and np.all(got[shift + count:] == guard)
+    ids_only = torch.full((count + 8,), guard, dtype=torch.int32, device="cuda")
+    mgpu.transform_lbs(count, dev(seg), want_ranks=False,
+                       out_seg=ids_only[rank_shift:rank_shift + count])
+    got = ids_only.cpu().numpy()
+    assert np.array_equal(got[rank_shift:rank_shift + count], want_seg)
+    assert np.all(got[:rank_shift] == guard)
+    assert np.all(got[rank_shift + count:] == guard)
+
+
+@pytest.mark.parametrize("dtype,shift", [(torch.float32, 1), (torch.float32, 3),
+                                         (torch.float64, 1), (torch.int64, 0)])
+def test_interval_expand_unaligned_output(mgpu, oracle, dtype, shift):
+    rng = np.random.default_rng(shift)
+    count, num_segments = 600_001, 40_000
+    seg = np.zeros(num_segments, dtype=np.int32)
+    seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
+    vals = torch.from_numpy(rng.integers(1, 120, size=num_segments)).to(dtype)
+    buf = torch.zeros(count + 8, dtype=dtype, device="cuda")
+    mgpu.interval_expand(vals.cuda(), count, dev(seg),
+                         out=buf[shift:shift + count])
+    got = buf.cpu().numpy()
+    want = oracle.interval_expand(vals.numpy(), count, seg)
+    assert np.array_equal(got[shift:shift + count], want)
+    assert np.all(got[:shift] == 0) and np.all(got[shift + count:] == 0)
+
+
 @pytest.mark.parametrize("dtype", [torch.uint8, torch.int16, torch.float32,
                                    torch.float64, torch.int64])
 def test_interval_expand(mgpu, oracle, dtype):

@@ -113,6 +113,65 @@ def test_reference_test_shape_long_segments(mgpu, oracle):
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("dtype", [np.int32, np.int64, np.float32, np.float64])
+@pytest.mark.parametrize("length", [8, 16, 24, 31, 32, 33, 64, 100, 128])
+def test_equal_length_segments(mgpu, oracle, dtype, length):
+    """Rows of one fixed width: tiles whose segment starts all sit at the same
+    position modulo 8 keep their run ends in shifted slots (no shared-memory
+    bank holds them all); the other widths take the plain path. A tile's first
+    item falls anywhere in a 16-byte granule of the input, so the starts'
+    positions within the staged tile differ from tile to tile."""
+    rng = np.random.default_rng(length)
+    count = 1_000_003
+    n = count // length
+    seg = (np.arange(n, dtype=np.int64) * length).astype(np.int32)
+    if np.issubdtype(dtype, np.integer):
+        values = rng.integers(-1000, 1000, size=count + 3).astype(dtype)
+        for off in (0, 1, 3):
+            check_exact(mgpu, oracle, values[off:off + count], seg, "plus",
+                        dtype(-7))
+        check_exact(mgpu, oracle, values[:count], seg, "max", dtype(-7))
+    else:
+        values = (rng.random(count + 3) * 2 - 1).astype(dtype)
+        tol = FP32_TOL if dtype == np.float32 else FP64_TOL
+        for off in (0, 1):
+            check_sum(mgpu, oracle, values[off:off + count], seg, -7.0, tol)
+        check_exact(mgpu, oracle, values[:count], seg, "min", dtype(-7))
+
+
+def test_equal_length_rows_with_empty_rows_and_one_long_row(mgpu, oracle):
+    """Fixed-width rows mixed with runs of empty rows (equal starts) and one
+    row that spans several tiles: aligned and unaligned tiles alternate, and a
+    shifted tile may be the one that closes a segment opened tiles before."""
+    rng = np.random.default_rng(5)
+    starts, at = [], 0
+    for block in range(400):
+        kind = block % 4
+        if kind == 0:
+            for _ in range(300):
+                starts.append(at)
+                at += 32
+        elif kind == 1:
+            starts += [at] * 50          # empty rows
+            starts.append(at)
+            at += 20_000                 # one long row
+        elif kind == 2:
+            for _ in range(500):
+                starts.append(at)
+                at += 16
+        else:
+            for _ in range(200):
+                starts.append(at)
+                at += int(rng.integers(1, 60))
+    count = at + 5
+    seg = np.array(starts, dtype=np.int32)
+    values = rng.integers(-50, 50, size=count).astype(np.int32)
+    check_exact(mgpu, oracle, values, seg, "plus", -1)
+    fvalues = (rng.random(count) * 2 - 1).astype(np.float32)
+    check_sum(mgpu, oracle, fvalues, seg, 0.0, FP32_TOL)
+    check_exact(mgpu, oracle, fvalues.astype(np.float64), seg, "max", -9.0)
+
+
 def test_many_empty_segments(mgpu, oracle):
     rng = np.random.default_rng(5)
     count, num_segments = 5000, 200_000
