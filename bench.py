@@ -832,7 +832,8 @@ def run_ours(args, rank, world, local_rank):
     mailbox = None
     if world > 1 and args.exchange == "p2p":
         try:
-            mailbox = sharded.Mailbox(side_stream=not args.no_side_stream)
+            mailbox = sharded.Mailbox(side_stream=not args.no_side_stream,
+                                      fused=not args.unfused)
         except sharded.MailboxError as e:
             # All ranks fail together; the records then travel by all-gather.
             print("bench: %s; using --exchange nccl" % e, file=sys.stderr)
@@ -1015,7 +1016,8 @@ def run_ours(args, rank, world, local_rank):
             secondary += config5_legs(args, rank, world, device, side_steps)
 
     if rank == 0:
-        launches_per_step = 2 if world == 1 else 4
+        launches_per_step = 4 if world > 1 and (
+            args.unfused or args.exchange != "p2p") else 2
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -1187,6 +1189,10 @@ def main():
                         help="multi-GPU, p2p: post the boundary records on "
                              "the main stream, in front of the reduction, "
                              "instead of on a side stream beside it")
+    parser.add_argument("--unfused", action="store_true",
+                        help="multi-GPU, p2p: post and collect as launches "
+                             "of their own (four per step) instead of inside "
+                             "the partitioner's and the reduction's")
     parser.add_argument("--impl", default="ours",
                         choices=["ours", "reference", "reference-cuda"])
     args = parser.parse_args()

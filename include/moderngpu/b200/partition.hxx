@@ -66,15 +66,33 @@ struct is_int_array {
 // and takes every remaining diagonal. Short runs of diagonals are written by
 // the thread itself; a long run (one segment spanning many tiles) is handed
 // to the whole warp at the end so it does not serialise on one thread.
-template<int nt, int per_thread, typename segments_it, typename int_t>
+// A partitioner launch can carry a few extra CTAs that do unrelated work which
+// must precede the dependent kernel anyway (the multi-GPU layer posts a
+// shard's boundary record this way instead of in a launch of its own):
+// tail_t::ctas CTAs are appended to the grid and CTA k of them runs tail(k)
+// with the partitioner's nt threads.
+struct no_partition_tail_t {
+  enum { ctas = 0 };
+  MGPU_DEVICE void operator()(int) const { }
+};
+
+template<int nt, int per_thread, typename segments_it, typename int_t,
+  typename tail_t>
 __global__ void __launch_bounds__(nt)
 lbs_partition_k(segments_it segments, int count, int num_segments,
   uint32_t step, int num_partitions, int_t* partitions,
   uint32_t* clear_head, int clear_head_words,
-  uint32_t* clear_tiles, int words_per_tile, int tile_stride) {
+  uint32_t* clear_tiles, int words_per_tile, int tile_stride, tail_t tail) {
 
   // Let a dependent kernel (the reduction) set itself up meanwhile.
   ptx::grid_launch_dependents();
+  if constexpr (tail_t::ctas > 0) {
+    const int first_tail = (int)gridDim.x - (int)tail_t::ctas;
+    if((int)blockIdx.x >= first_tail) {
+      tail((int)blockIdx.x - first_tail);
+      return;
+    }
+  }
   const unsigned full = 0xffffffffu;
   const int lane = (int)(threadIdx.x & 31);
   const uint32_t total = (uint32_t)count + (uint32_t)num_segments;
@@ -181,22 +199,25 @@ lbs_partition_k(segments_it segments, int count, int num_segments,
 }
 
 // Enqueue the partition kernel. `partitions` holds num_partitions entries.
-template<typename segments_it, typename int_t>
+enum { lbs_partition_threads = 128 };
+
+template<typename segments_it, typename int_t,
+  typename tail_t = no_partition_tail_t>
 void launch_lbs_partition(segments_it segments, int count, int num_segments,
   int64_t spacing, int num_partitions, int_t* partitions, cudaStream_t stream,
   uint32_t* clear_head = nullptr, int clear_head_words = 0,
   uint32_t* clear_tiles = nullptr, int words_per_tile = 0,
-  int tile_stride = 0) {
-  enum { nt = 128, per_thread = 16 };
+  int tile_stride = 0, tail_t tail = tail_t()) {
+  enum { nt = lbs_partition_threads, per_thread = 16 };
   // One more index than there are segments: the virtual closing start.
   int num_ctas = (int)div_up((int64_t)num_segments + 1,
     (int64_t)(nt * per_thread));
   uint32_t step = (uint32_t)(spacing < 0x7fffffff ? spacing : 0x7fffffff);
   if(num_partitions > 0)
-    lbs_partition_k<nt, per_thread><<<num_ctas, nt, 0, stream>>>(segments,
-      count, num_segments, step, num_partitions, partitions, clear_head,
-      clear_head_words, clear_tiles, words_per_tile,
-      tile_stride ? tile_stride : words_per_tile);
+    lbs_partition_k<nt, per_thread><<<num_ctas + (int)tail_t::ctas, nt, 0,
+      stream>>>(segments, count, num_segments, step, num_partitions,
+      partitions, clear_head, clear_head_words, clear_tiles, words_per_tile,
+      tile_stride ? tile_stride : words_per_tile, tail);
 }
 
 } // namespace detail

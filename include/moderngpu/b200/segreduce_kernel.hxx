@@ -190,8 +190,19 @@ struct tile_desc_t {
   int pad;
 };
 
+// A reduction can end with one piece of work that needs every output of the
+// call: finish_t::active makes the CTAs count themselves out, and the thread
+// that finds itself last -- every output is then written and visible to it --
+// runs finish() once (the multi-GPU layer folds the following shards'
+// boundary partials into the shard's last output this way instead of in a
+// launch of its own).
+struct no_finish_t {
+  enum { active = 0 };
+  MGPU_DEVICE void operator()() const { }
+};
+
 template<typename type_t, typename source_t, typename segments_it,
-  typename output_it, typename op_t>
+  typename output_it, typename op_t, typename finish_t = no_finish_t>
 struct segreduce_args_t {
   source_t source;
   segments_it segments;
@@ -200,9 +211,10 @@ struct segreduce_args_t {
   type_t init;
   int count, num_segments, num_tiles;
   const int* partitions;
-  uint32_t* header;       // [0] ticket counter, [1] status
+  uint32_t* header;       // [0] ticket counter, [1] status, [2] CTAs done
   void* tile_state;
   uint64_t timeout_ns;    // bound on every device-side wait
+  finish_t finish;
 };
 
 // What a finished tile leaves for the CTA's carry warp: enough to finish the
@@ -280,11 +292,12 @@ MGPU_DEVICE void load_chunk(const type_t* src, type_t (&v)[vt]) {
 }
 
 template<typename tuning_t, typename type_t, typename source_t,
-  typename segments_it, typename output_it, typename op_t>
+  typename segments_it, typename output_it, typename op_t,
+  typename finish_t = no_finish_t>
 __global__ void __launch_bounds__(tuning_t::nt + 32 + 32 * segreduce_carry_warps,
   tuning_t::occ)
 segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
-  op_t> args) {
+  op_t, finish_t> args) {
 
   typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk> layout_t;
   typedef typename layout_t::fixed_t fixed_t;
@@ -553,6 +566,16 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           if(need_left && have) result = has_lead ? op(carry, lead) : carry;
           args.output[e.b0 - 1] = result;
         }
+      }
+    }
+    if constexpr (finish_t::active) {
+      // This warp's outputs, then its count; the consumers count separately.
+      __threadfence();
+      __syncwarp();
+      if(0 == lane &&
+        2 * gridDim.x - 1 == atomicAdd(args.header + 2, 1u)) {
+        __threadfence();
+        args.finish();
       }
     }
     return;
@@ -993,6 +1016,15 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       ptx::mbar_arrive(&fixed.edge_full[r]);
     }
   }
+  if constexpr (finish_t::active) {
+    // Every consumer's outputs, then one count for all of them.
+    __threadfence();
+    ptx::named_sync<1, nt>();
+    if(0 == tid && 2 * gridDim.x - 1 == atomicAdd(args.header + 2, 1u)) {
+      __threadfence();
+      args.finish();
+    }
+  }
 }
 
 ////////////////////////////////////////////////////////////////////////////////
@@ -1041,16 +1073,25 @@ constexpr uint64_t default_timeout_ns = 2000000000ull;
 // Enqueue partitioner + reduction on `stream`. `workspace` must hold
 // segreduce_plan_t<...>(count, num_segments).bytes bytes, 128-byte aligned.
 // `after_partition`, when given, is recorded between the two kernels.
+// `tail` rides in the partitioner's launch and `finish` ends the reduction
+// (see no_partition_tail_t, no_finish_t). `parts`: 1 enqueues the partitioner
+// only, 2 the reduction only (the partitioner of the same call must precede
+// it in the stream), 3 both.
+enum { segreduce_partition_part = 1, segreduce_reduce_part = 2,
+  segreduce_both_parts = 3 };
+
 template<typename tuning_t, typename type_t, typename source_t,
-  typename segments_it, typename output_it, typename op_t>
+  typename segments_it, typename output_it, typename op_t,
+  typename tail_t = no_partition_tail_t, typename finish_t = no_finish_t>
 void segreduce_enqueue(source_t source, int count, segments_it segments,
   int num_segments, output_it output, op_t op, type_t init, void* workspace,
   cudaStream_t stream, uint64_t timeout_ns = default_timeout_ns,
-  cudaEvent_t after_partition = nullptr) {
+  cudaEvent_t after_partition = nullptr, tail_t tail = tail_t(),
+  finish_t finish = finish_t(), int parts = segreduce_both_parts) {
 
   typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk> layout_t;
-  typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t>
-    args_t;
+  typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t,
+    finish_t> args_t;
   segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);
   if(!plan.num_tiles) return;
 
@@ -1059,22 +1100,24 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
   int* partitions = (int*)(base + plan.partitions_offset);
   void* state = base + plan.state_offset;
 
-  launch_lbs_partition(segments, count, num_segments,
-    (int64_t)tuning_t::nv, plan.num_tiles + 1, partitions, stream,
-    header, 32, (uint32_t*)state,
-    (int)tile_state_traits<type_t>::clear_words,
-    (int)tile_state_traits<type_t>::stride_words);
+  if(parts & segreduce_partition_part)
+    launch_lbs_partition(segments, count, num_segments,
+      (int64_t)tuning_t::nv, plan.num_tiles + 1, partitions, stream,
+      header, 32, (uint32_t*)state,
+      (int)tile_state_traits<type_t>::clear_words,
+      (int)tile_state_traits<type_t>::stride_words, tail);
   if(after_partition) cudaEventRecord(after_partition, stream);
+  if(!(parts & segreduce_reduce_part)) return;
 
   auto kernel = segreduce_k<tuning_t, type_t, source_t, segments_it,
-    output_it, op_t>;
+    output_it, op_t, finish_t>;
   int threads = tuning_t::nt + 32 + 32 * segreduce_carry_warps;
   int resident = resident_ctas<tuple<tuning_t, args_t> >(kernel, threads,
     (int)layout_t::total_bytes);
   int grid = plan.num_tiles < resident ? plan.num_tiles : resident;
 
   args_t args { source, segments, output, op, init, count, num_segments,
-    plan.num_tiles, partitions, header, state, timeout_ns };
+    plan.num_tiles, partitions, header, state, timeout_ns, finish };
   // Launched as a programmatic dependent of the partitioner: its CTAs start,
   // initialise their barriers and wait inside the kernel.
   cudaLaunchConfig_t config = { };

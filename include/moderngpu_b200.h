@@ -352,6 +352,44 @@ int mgpu_b200_shard_fold(int dtype, int op, const void* records_device,
   int rank, int world, void* out_device, int num_starts,
   const void* init_host, void* stream);
 
+/*
+ * The fused step: what mgpu_b200_shard_post + mgpu_b200_segreduce +
+ * mgpu_b200_shard_collect do in four launches, in two (no counterpart in the
+ * reference; the C++ form is mgpu::sharded_segreduce, include/moderngpu/
+ * kernel_sharded.hxx).
+ *
+ * mgpu_b200_shard_begin enqueues the merge-path partitioner of the shard's
+ * reduction; a few extra CTAs of the same launch fold the shard's leading
+ * items and store the boundary record into the mailboxes (as
+ * mgpu_b200_shard_post), and tell the GPUs that hold later shards that this
+ * shard is done with step - 1. mgpu_b200_shard_finish enqueues the reduction
+ * kernel; its last CTA to finish folds the following shards' records into
+ * out[num_starts - 1] (as mgpu_b200_shard_collect, same bounded wait and
+ * status word). The two calls of a shard take the same arguments, stream and
+ * workspace (mgpu_b200_segreduce_workspace_bytes(dtype, count, num_starts)
+ * bytes, 128-byte aligned, one per shard). A GPU that holds several shards
+ * calls _begin for all of them, in shard order, before the first _finish: a
+ * shard's collect may need the record of a later shard of the same GPU.
+ * `step` counts from 1, the same on every GPU; a GPU may run at most 63 steps
+ * ahead of a GPU that reads its records.
+ */
+int mgpu_b200_shard_begin(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* workspace_device,
+  size_t workspace_bytes, void* mailbox_device,
+  const void* const* peers_device, int shard, int num_shards,
+  int shards_per_gpu, unsigned step, uint64_t timeout_ns, void* stream);
+
+int mgpu_b200_shard_finish(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* out_device,
+  const void* init_host, void* workspace_device, size_t workspace_bytes,
+  void* mailbox_device, const void* const* peers_device, int shard,
+  int num_shards, int shards_per_gpu, unsigned step, uint64_t timeout_ns,
+  void* stream);
+
+/* Returns a mailbox's status word to 0 (enqueued on `stream`), so that a
+ * later wait that runs out can be told from an earlier one. */
+int mgpu_b200_mailbox_clear_status(void* mailbox_device, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

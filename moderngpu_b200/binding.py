@@ -167,6 +167,18 @@ def _declare_optional(lib):
     lib.mgpu_b200_shard_collect.argtypes = [
         c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, ctypes.c_uint,
         c_void_p, c_int, c_void_p, ctypes.c_uint64, c_void_p]
+    lib.mgpu_b200_shard_begin.restype = c_int
+    lib.mgpu_b200_shard_begin.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_size_t,
+        c_void_p, c_void_p, c_int, c_int, c_int, ctypes.c_uint,
+        ctypes.c_uint64, c_void_p]
+    lib.mgpu_b200_shard_finish.restype = c_int
+    lib.mgpu_b200_shard_finish.argtypes = [
+        c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+        c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int,
+        ctypes.c_uint, ctypes.c_uint64, c_void_p]
+    lib.mgpu_b200_mailbox_clear_status.restype = c_int
+    lib.mgpu_b200_mailbox_clear_status.argtypes = [c_void_p, c_void_p]
     lib.mgpu_b200_shard_fold.restype = c_int
     lib.mgpu_b200_shard_fold.argtypes = [
         c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,

@@ -10,117 +10,34 @@
 // START inside the shard. out[0] is therefore the shard's boundary partial
 // (or `init` when the shard's first real segment starts at item 0).
 #include <moderngpu_b200.h>
-#include <cuda_runtime.h>
+#include <moderngpu/kernel_sharded.hxx>
 #include <cstring>
 
 namespace {
 
-enum : uint32_t {
-  shard_has_partial = 1,   // out[0] folds at least one item
-  shard_has_start = 2,     // at least one segment starts inside the shard
-  shard_last_empty = 4     // the last local segment has no local item
-};
+// Record format, mailbox layout and the bounded waits: include/moderngpu/
+// b200/shard.hxx, shared with the C++ entry point mgpu::sharded_segreduce.
+using mgpu::detail::shard_has_partial;
+using mgpu::detail::shard_has_start;
+using mgpu::detail::shard_last_empty;
+using mgpu::detail::shard_record_t;
+using mgpu::detail::mailbox_t;
+using mgpu::detail::mailbox_ring;
+using mgpu::detail::mailbox_max_shards;
+using mgpu::detail::mailbox_scratch_offset;
+using mgpu::detail::mailbox_used_bytes;
+using mgpu::detail::mailbox_alloc_bytes;
+using mgpu::detail::status_record_timeout;
+using mgpu::detail::status_slot_timeout;
+typedef mgpu::detail::shard_chain_t chain_t;
 
-struct shard_record_t {
-  unsigned long long value;   // the partial's bits, zero-padded to 8 bytes
-  uint32_t flags;
-  uint32_t seq;               // mailbox only: the step the record belongs to
-};
-
-// Mailbox: one block of device memory per GPU that the other GPUs of the box
-// map (CUDA IPC) and write into over NVLink. Fixed layout:
-//   [0, 256)        status word (0 = fine, 3 = a record did not arrive in
-//                   time, 4 = a ring slot was not released in time)
-//   [256, 1280)     scratch of the leading-items reduction
-//   [1280, 9472)    acks: shard v's last finished step, one 128-byte line each,
-//                   written by the GPU that holds shard v
-//   [9472, ...)     slots[shard][step % ring]: 32-byte records written by the
-//                   GPU that holds the shard
-// A record travels as three 8-byte words that each carry the step number in
-// their upper half next to 32 bits of payload (value low, value high, flags):
-// every word is one atomic store, so the reader needs no fence -- it polls
-// its OWN memory until all three words show the step it waits for. No kernel
-// ever polls another GPU's memory.
-enum {
-  mailbox_ring = 64, mailbox_max_shards = 64,
-  mailbox_scratch_offset = 256, mailbox_ack_offset = 1280,
-  mailbox_slot_offset = mailbox_ack_offset + 128 * mailbox_max_shards,
-  mailbox_slot_bytes = 32,
-  mailbox_used_bytes = mailbox_slot_offset +
-    mailbox_slot_bytes * mailbox_ring * mailbox_max_shards,
-  mailbox_alloc_bytes = 2 << 20,   // a whole allocation block of its own
-  status_record_timeout = 3, status_slot_timeout = 4
-};
-
-struct mailbox_t {
-  char* base;
-  __device__ uint32_t* status() const { return (uint32_t*)base; }
-  __device__ volatile uint32_t* ack(int shard) const {
-    return (volatile uint32_t*)(base + mailbox_ack_offset + 128 * shard);
-  }
-  __device__ volatile unsigned long long* slot(int shard, uint32_t step) const {
-    return (volatile unsigned long long*)(base + mailbox_slot_offset +
-      mailbox_slot_bytes * (shard * mailbox_ring + step % mailbox_ring));
-  }
-};
-
-// What a posting / collecting kernel needs to know about the chain of shards.
-// peers[p] is GPU p's mailbox as mapped into this GPU's address space (this
-// GPU's own mailbox at its own index). Shard v lives on GPU v / per_gpu.
-struct chain_t {
-  char* const* peers;       // null: no mailbox, write `record` only
-  int shard, num_shards, per_gpu;
-  uint32_t step;
-  unsigned long long timeout_ns;
-};
-
-__device__ __forceinline__ unsigned long long timer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// Waits, for at most timeout_ns, until this GPU's copy of the record of
-// (shard, step) is complete. Returns false when time ran out.
 __device__ bool wait_record(const mailbox_t& box, int shard, uint32_t step,
   unsigned long long timeout_ns, shard_record_t& got) {
-  volatile unsigned long long* word = box.slot(shard, step);
-  unsigned long long begin = 0;
-  for(unsigned spin = 0; ; ++spin) {
-    unsigned long long w0 = word[0], w1 = word[1], w2 = word[2];
-    if((uint32_t)(w0 >> 32) == step && (uint32_t)(w1 >> 32) == step &&
-      (uint32_t)(w2 >> 32) == step) {
-      got.value = (w0 & 0xffffffffull) | (w1 << 32);
-      got.flags = (uint32_t)w2;
-      got.seq = step;
-      return true;
-    }
-    if(0 == (spin & 63)) {
-      unsigned long long now = timer_ns();
-      if(!begin) begin = now;
-      else if(now - begin > timeout_ns) return false;
-    }
-  }
+  return mgpu::detail::mailbox_wait_record(box, shard, step, timeout_ns, got);
 }
-
-// Waits until every shard held by GPU `gpu` has finished step `step - ring`,
-// i.e. until the ring slot about to be overwritten there is no longer read.
 __device__ bool wait_slot_free(const mailbox_t& box, const chain_t& chain,
   int gpu) {
-  if(chain.step <= (uint32_t)mailbox_ring) return true;
-  const uint32_t need = chain.step - mailbox_ring;
-  const int v_end = min((gpu + 1) * chain.per_gpu, chain.num_shards);
-  unsigned long long begin = 0;
-  for(int v = gpu * chain.per_gpu; v < v_end; ++v) {
-    for(unsigned spin = 0; ; ++spin) {
-      if((int)(*box.ack(v) - need) >= 0) break;
-      if(0 == (spin & 63)) {
-        unsigned long long now = timer_ns();
-        if(!begin) begin = now;
-        else if(now - begin > chain.timeout_ns) return false;
-      }
-    }
-  }
-  return true;
+  return mgpu::detail::mailbox_wait_slot_free(box, chain, gpu);
 }
 
 template<typename type_t>
@@ -402,12 +319,71 @@ __global__ void shard_collect_k(char* mailbox, chain_t chain, int op,
   }
 }
 
-// How long a kernel waits for another GPU's record or ack before it gives up.
-const unsigned long long default_mailbox_wait_ns = 10000000000ull;
+using mgpu::detail::default_mailbox_wait_ns;
 
 inline int code_of(cudaError_t e) {
   return cudaSuccess == e ? MGPU_B200_OK : MGPU_B200_E_CUDA + (int)e;
 }
+
+} // namespace
+
+namespace {
+
+// The fused step (mgpu_b200_shard_begin / _finish): the shard's partitioner
+// with the post riding in its launch, and the shard's reduction with the
+// collect as its last act -- the same kernels mgpu::sharded_segreduce runs.
+template<typename type_t, typename op_t>
+int fused_typed(int parts, const void* input, int count, const int* starts,
+  int num_starts, void* out, const void* init_host, void* workspace,
+  void* mailbox, const void* const* peers, int shard, int num_shards,
+  int per_gpu, unsigned step, uint64_t timeout_ns, cudaStream_t stream) {
+  using namespace mgpu;
+  typedef typename detail::segreduce_default_tuning<type_t>::type tuning_t;
+  type_t init = type_t();
+  if(init_host) memcpy(&init, init_host, sizeof(type_t));
+  chain_t chain = { (char* const*)peers, shard, num_shards, per_gpu, step,
+    timeout_ns ? timeout_ns : default_mailbox_wait_ns };
+  detail::shard_post_tail_t<type_t, op_t> tail = { (const type_t*)input,
+    starts, num_starts, count, op_t(), chain, (char*)mailbox };
+  detail::shard_collect_finish_t<type_t, op_t> finish = { (char*)mailbox,
+    chain, op_t(), (type_t*)out, num_starts, init };
+  try {
+    detail::segreduce_enqueue<tuning_t>(
+      detail::array_source_t<type_t> { (const type_t*)input }, count, starts,
+      num_starts, (type_t*)out, op_t(), init, workspace, stream,
+      detail::default_timeout_ns, nullptr, tail, finish, parts);
+  } catch(cuda_exception_t& e) {
+    return MGPU_B200_E_CUDA + (int)e.result;
+  }
+  cudaError_t e = cudaGetLastError();
+  return cudaSuccess == e ? MGPU_B200_OK : MGPU_B200_E_CUDA + (int)e;
+}
+
+template<typename type_t>
+int fused_op(int op, int parts, const void* input, int count,
+  const int* starts, int num_starts, void* out, const void* init_host,
+  void* workspace, void* mailbox, const void* const* peers, int shard,
+  int num_shards, int per_gpu, unsigned step, uint64_t timeout_ns,
+  cudaStream_t stream) {
+  switch(op) {
+    case MGPU_B200_PLUS: return fused_typed<type_t, mgpu::plus_t<type_t> >(
+      parts, input, count, starts, num_starts, out, init_host, workspace,
+      mailbox, peers, shard, num_shards, per_gpu, step, timeout_ns, stream);
+    case MGPU_B200_MAX: return fused_typed<type_t, mgpu::maximum_t<type_t> >(
+      parts, input, count, starts, num_starts, out, init_host, workspace,
+      mailbox, peers, shard, num_shards, per_gpu, step, timeout_ns, stream);
+    case MGPU_B200_MIN: return fused_typed<type_t, mgpu::minimum_t<type_t> >(
+      parts, input, count, starts, num_starts, out, init_host, workspace,
+      mailbox, peers, shard, num_shards, per_gpu, step, timeout_ns, stream);
+  }
+  return MGPU_B200_E_UNSUPPORTED;
+}
+
+int fused_dispatch(int dtype, int op, int parts, const void* input, int count,
+  const int* starts, int num_starts, void* out, const void* init_host,
+  void* workspace, size_t workspace_bytes, void* mailbox,
+  const void* const* peers, int shard, int num_shards, int per_gpu,
+  unsigned step, uint64_t timeout_ns, void* stream);
 
 } // namespace
 
@@ -620,4 +596,65 @@ int mgpu_b200_shard_fold(int dtype, int op, const void* records_device,
   return code_of(cudaGetLastError());
 }
 
+int mgpu_b200_shard_begin(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* workspace_device,
+  size_t workspace_bytes, void* mailbox_device,
+  const void* const* peers_device, int shard, int num_shards,
+  int shards_per_gpu, unsigned step, uint64_t timeout_ns, void* stream) {
+  return fused_dispatch(dtype, op, mgpu::detail::segreduce_partition_part,
+    input_device, count, starts_device, num_starts, nullptr, nullptr,
+    workspace_device, workspace_bytes, mailbox_device, peers_device, shard,
+    num_shards, shards_per_gpu, step, timeout_ns, stream);
+}
+
+int mgpu_b200_shard_finish(int dtype, int op, const void* input_device,
+  int count, const int* starts_device, int num_starts, void* out_device,
+  const void* init_host, void* workspace_device, size_t workspace_bytes,
+  void* mailbox_device, const void* const* peers_device, int shard,
+  int num_shards, int shards_per_gpu, unsigned step, uint64_t timeout_ns,
+  void* stream) {
+  if(!out_device || !init_host) return MGPU_B200_E_INVALID;
+  return fused_dispatch(dtype, op, mgpu::detail::segreduce_reduce_part,
+    input_device, count, starts_device, num_starts, out_device, init_host,
+    workspace_device, workspace_bytes, mailbox_device, peers_device, shard,
+    num_shards, shards_per_gpu, step, timeout_ns, stream);
+}
+
+int mgpu_b200_mailbox_clear_status(void* mailbox_device, void* stream) {
+  if(!mailbox_device) return MGPU_B200_E_INVALID;
+  return code_of(cudaMemsetAsync(mailbox_device, 0, 4, (cudaStream_t)stream));
+}
+
 } // extern "C"
+
+namespace {
+int fused_dispatch(int dtype, int op, int parts, const void* input, int count,
+  const int* starts, int num_starts, void* out, const void* init_host,
+  void* workspace, size_t workspace_bytes, void* mailbox,
+  const void* const* peers, int shard, int num_shards, int per_gpu,
+  unsigned step, uint64_t timeout_ns, void* stream) {
+  if(!starts || num_starts < 1 || count < 0 || (count && !input) ||
+    !workspace || (uintptr_t)workspace % 128 ||
+    !chain_ok(mailbox, peers, shard, num_shards, per_gpu, step))
+    return MGPU_B200_E_INVALID;
+  size_t need = mgpu_b200_segreduce_workspace_bytes(dtype, count, num_starts);
+  if(!need) return MGPU_B200_E_UNSUPPORTED;
+  if(workspace_bytes < need) return MGPU_B200_E_WORKSPACE;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch(dtype) {
+    case MGPU_B200_F32: return fused_op<float>(op, parts, input, count,
+      starts, num_starts, out, init_host, workspace, mailbox, peers, shard,
+      num_shards, per_gpu, step, timeout_ns, s);
+    case MGPU_B200_F64: return fused_op<double>(op, parts, input, count,
+      starts, num_starts, out, init_host, workspace, mailbox, peers, shard,
+      num_shards, per_gpu, step, timeout_ns, s);
+    case MGPU_B200_I32: return fused_op<int>(op, parts, input, count, starts,
+      num_starts, out, init_host, workspace, mailbox, peers, shard,
+      num_shards, per_gpu, step, timeout_ns, s);
+    case MGPU_B200_I64: return fused_op<long long>(op, parts, input, count,
+      starts, num_starts, out, init_host, workspace, mailbox, peers, shard,
+      num_shards, per_gpu, step, timeout_ns, s);
+  }
+  return MGPU_B200_E_UNSUPPORTED;
+}
+} // namespace

@@ -1,32 +1,39 @@
 """Multi-GPU segmented reduction: one process per GPU, the item range cut
-evenly across ranks, one 16-byte boundary record exchanged per rank.
+evenly across ranks, one 16-byte boundary record exchanged per shard and step.
 
 The reference is single-device (src/moderngpu/context.hxx:85,109-110 knows one
-stream on the current device); this layer is new. Data path per rank:
+stream on the current device); this layer is new. It binds the C ABI's shard
+entry points for the one-process-per-GPU case; a C++ program that drives
+several GPUs from one process uses mgpu::sharded_segreduce
+(include/moderngpu/kernel_sharded.hxx), which runs the same kernels.
 
-  1. mgpu_b200_shard_lead: fold of the shard's leading items (those before
-     its first segment start) + flags -> 16-byte boundary record;
-  2. torch.distributed all_gather of the records (16 bytes per rank -- the
-     only exchange; NVLink carries it when the backend is NCCL), started
-     asynchronously so that it overlaps step 3;
-  3. mgpu_b200_segreduce on the shard (items, shard-local start table);
-  4. mgpu_b200_shard_fold: the rank that owns a straddling segment folds the
-     following ranks' partials into its last output, in rank order.
+Default data path (with a `Mailbox`; no collective anywhere in it), two
+launches per shard and step:
 
-With overlap=False the record is taken from the reduction's own first output
-instead (mgpu_b200_shard_pack) and the exchange follows the reduction.
+  1. mgpu_b200_shard_begin: the partitioner of the shard's reduction; a few
+     extra CTAs of the same launch fold the shard's leading items (those
+     before its first segment start) and store the record straight into the
+     memory of the GPUs that hold earlier shards -- peer-to-peer stores over
+     NVLink into memory mapped with CUDA IPC;
+  2. mgpu_b200_shard_finish: the reduction kernel on (items, shard-local
+     start table); its last CTA to finish waits -- in its own GPU's memory,
+     for a bounded time -- for the following shards' records and folds them
+     into the shard's last output, in shard order.
 
-With a `Mailbox` the exchange needs no collective at all: step 1 becomes
-mgpu_b200_shard_post, which stores the record straight into the memory of
-the GPUs that hold earlier shards (peer-to-peer stores over NVLink into
-memory mapped with CUDA IPC), step 2 disappears, and step 4 becomes
-mgpu_b200_shard_collect, which waits -- in its own GPU's memory, for a
-bounded time -- for the records it needs.
+`Mailbox(fused=False)` runs the same exchange as four launches
+(mgpu_b200_shard_post, the reduction's two, mgpu_b200_shard_collect).
+
+Without a mailbox the records travel by one torch.distributed all_gather of
+16 bytes per rank: mgpu_b200_shard_lead (record from the leading items, the
+all-gather overlapping the reduction) or, with overlap=False,
+mgpu_b200_shard_pack (record from the reduction's first output), then
+mgpu_b200_shard_fold on the owner.
 
 Shard-local start table: entry 0 is always 0 and stands for the segment
 carried in from the previous rank; the remaining entries are the local offsets
 of the segments that START inside the shard. `shard_table` derives it from a
-global start table.
+global start table on the host; mgpu::sharded_partition does it on the
+devices.
 """
 import ctypes
 
@@ -117,9 +124,13 @@ class Mailbox:
     (collective) when done."""
 
     def __init__(self, group=None, shards_per_gpu=1, device=None,
-                 timeout_ns=0, side_stream=True):
+                 timeout_ns=0, side_stream=True, fused=True):
         lib = binding.load_library()
         self.lib = lib
+        # fused: two launches per shard and step (post and collect ride in the
+        # partitioner's and the reduction's launches); otherwise four.
+        self.fused = fused
+        self._spaces = []
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -198,6 +209,26 @@ class Mailbox:
     def next_step(self):
         self.step += 1
         return self.step
+
+    def workspaces(self, sizes):
+        """One scratch buffer per shard of this rank (the fused step keeps
+        every shard's partition table until its reduction has run)."""
+        while len(self._spaces) < len(sizes):
+            self._spaces.append(None)
+        for j, need in enumerate(sizes):
+            buf = self._spaces[j]
+            if buf is None or buf.numel() < need:
+                self._spaces[j] = torch.empty(max(need, 1 << 20),
+                                              dtype=torch.uint8,
+                                              device=self.device)
+        return self._spaces[:len(sizes)]
+
+    def clear_status(self):
+        """Status word back to 0 (enqueued on the current stream), so that
+        a later wait that runs out can be told from an earlier one."""
+        with torch.cuda.device(self.device):
+            binding._check(self.lib.mgpu_b200_mailbox_clear_status(
+                self.own, binding._stream(self.device)))
 
     def status(self):
         """0, or the code of the first bounded wait that ran out (3: a record
@@ -299,7 +330,52 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records,
 
 
 def _sharded_mailbox(shards, op, init, outs, workspace, mailbox):
-    """Post every shard's record, reduce every shard, collect."""
+    """The fused step: every shard's partitioner (its launch also posts the
+    shard's boundary record), then every shard's reduction (its last CTA
+    collects the following shards' records): two launches per shard."""
+    lib = mailbox.lib
+    k = len(shards)
+    if k != mailbox.per_gpu:
+        raise ValueError("the mailbox was set up for %d shards per GPU" %
+                         mailbox.per_gpu)
+    dev = shards[0][0].device
+    dtype = binding._DTYPES[shards[0][0].dtype]
+    stream = binding._stream(dev)
+    step = mailbox.next_step()
+    first = mailbox.rank * k
+    init_c = binding._CTYPES[shards[0][0].dtype](init)
+    results = []
+    with torch.cuda.device(dev):
+        spaces = mailbox.workspaces(
+            [lib.mgpu_b200_segreduce_workspace_bytes(
+                dtype, values.numel(), table.numel())
+             for values, table in shards])
+        for j, (values, table) in enumerate(shards):
+            binding._check(lib.mgpu_b200_shard_begin(
+                dtype, binding._OPS[op], values.data_ptr(), values.numel(),
+                table.data_ptr(), table.numel(), spaces[j].data_ptr(),
+                spaces[j].numel(), mailbox.own, mailbox.peers.data_ptr(),
+                first + j, mailbox.num_shards, k, step, mailbox.timeout_ns,
+                stream))
+        for j, (values, table) in enumerate(shards):
+            out = None if outs is None else outs[j]
+            if out is None:
+                out = torch.empty(table.numel(), dtype=values.dtype,
+                                  device=dev)
+            binding._check(lib.mgpu_b200_shard_finish(
+                dtype, binding._OPS[op], values.data_ptr(), values.numel(),
+                table.data_ptr(), table.numel(), out.data_ptr(),
+                ctypes.byref(init_c), spaces[j].data_ptr(), spaces[j].numel(),
+                mailbox.own, mailbox.peers.data_ptr(), first + j,
+                mailbox.num_shards, k, step, mailbox.timeout_ns, stream))
+            results.append(out)
+    return results
+
+
+def _sharded_mailbox_unfused(shards, op, init, outs, workspace, mailbox):
+    """The same exchange as four launches per shard (post, partitioner,
+    reduction, collect): kept for comparison and for callers that drive the
+    three entry points themselves."""
     lib = mailbox.lib
     k = len(shards)
     if k != mailbox.per_gpu:
@@ -314,9 +390,8 @@ def _sharded_mailbox(shards, op, init, outs, workspace, mailbox):
     results = []
     with torch.cuda.device(dev):
         # The posts depend on nothing the reductions produce: on the mailbox's
-        # side stream (the default) they run beside the partitioner and the
-        # first tiles instead of in front of them (2 GPUs: 202.3 -> 196.9 us
-        # per step).
+        # side stream they run beside the partitioner and the first tiles
+        # instead of in front of them.
         side = mailbox.side
         post_stream = stream
         if side is not None:
@@ -360,7 +435,10 @@ def sharded_segreduce_multi(shards, op="plus", init=0, group=None, outs=None,
     Returns the list of per-shard outputs. With `mailbox` the records travel
     by peer-to-peer stores and no collective runs."""
     if mailbox is not None:
-        return _sharded_mailbox(shards, op, init, outs, workspace, mailbox)
+        if mailbox.fused:
+            return _sharded_mailbox(shards, op, init, outs, workspace, mailbox)
+        return _sharded_mailbox_unfused(shards, op, init, outs, workspace,
+                                        mailbox)
     lib = binding.load_library()
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0

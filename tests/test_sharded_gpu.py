@@ -54,10 +54,12 @@ def worker(rank, world, port, kind, dtype_name, op, overlap, queue):
         begin, end, first, table = sharded.shard_table(seg, values.size, rank, world)
         v = torch.from_numpy(values[begin:end].copy()).cuda()
         t = torch.from_numpy(table).cuda()
-        if overlap == "mailbox":
+        if overlap in ("mailbox", "mailbox4"):
             # Peer-to-peer records, no collective in the data path; 70 steps
             # so that the 64-slot ring wraps and the acks are exercised.
-            box = sharded.Mailbox()
+            # "mailbox": the fused step (two launches); "mailbox4": post,
+            # reduction and collect as launches of their own.
+            box = sharded.Mailbox(fused=overlap == "mailbox")
             for _ in range(70):
                 out = sharded.sharded_segreduce(v, t, op=op, init=-7, mailbox=box)
             assert box.status() == 0
@@ -81,6 +83,8 @@ def worker(rank, world, port, kind, dtype_name, op, overlap, queue):
     ("lognormal", "float64", "max", "mailbox"), ("lognormal", "int64", "plus", "mailbox"),
     ("few_long", "int32", "plus", "mailbox"), ("one", "float64", "min", "mailbox"),
     ("lognormal", "float64", "plus", "mailbox"),
+    ("lognormal", "float64", "max", "mailbox4"), ("few_long", "int32", "plus", "mailbox4"),
+    ("one", "float64", "min", "mailbox4"),
 ])
 def test_sharded_matches_oracle(oracle, kind, dtype, op, overlap):
     world = min(torch.cuda.device_count(), 4)
@@ -110,7 +114,7 @@ def test_sharded_matches_oracle(oracle, kind, dtype, op, overlap):
         assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("overlap", [True, False, "mailbox"])
+@pytest.mark.parametrize("overlap", [True, False, "mailbox", "mailbox4"])
 @pytest.mark.parametrize("kind,dtype,op", [
     ("lognormal", "float64", "max"), ("few_long", "int64", "plus"),
     ("one", "int32", "plus"),
@@ -127,8 +131,8 @@ def test_several_shards_on_one_gpu(mgpu, oracle, kind, dtype, op, overlap):
         shards.append((torch.from_numpy(values[begin:end].copy()).cuda(),
                        torch.from_numpy(table).cuda()))
         firsts.append(first)
-    if overlap == "mailbox":
-        box = sharded.Mailbox(shards_per_gpu=pieces)
+    if overlap in ("mailbox", "mailbox4"):
+        box = sharded.Mailbox(shards_per_gpu=pieces, fused=overlap == "mailbox")
         for _ in range(3):
             outs = sharded.sharded_segreduce_multi(shards, op=op, init=-7,
                                                    mailbox=box)
@@ -225,6 +229,28 @@ def test_mailbox_waits_are_bounded(mgpu):
     assert box.status() == 4
     box.close()
 
+    # (c) the fused step: shard 0's reduction ends with the collect, and the
+    # record of shard 1 never comes. The reduction's own outputs stand.
+    box = sharded.Mailbox(shards_per_gpu=2)
+    dtype = binding._DTYPES[v.dtype]
+    need = lib.mgpu_b200_segreduce_workspace_bytes(dtype, v.numel(), t.numel())
+    space = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device="cuda")
+    fused_out = torch.full_like(before, -1)
+    binding._check(lib.mgpu_b200_shard_begin(
+        dtype, binding._OPS["plus"], v.data_ptr(), v.numel(), t.data_ptr(),
+        t.numel(), space.data_ptr(), space.numel(), box.own,
+        box.peers.data_ptr(), 0, 2, 2, 1, limit, binding._stream(v.device)))
+    binding._check(lib.mgpu_b200_shard_finish(
+        dtype, binding._OPS["plus"], v.data_ptr(), v.numel(), t.data_ptr(),
+        t.numel(), fused_out.data_ptr(), ctypes.byref(init), space.data_ptr(),
+        space.numel(), box.own, box.peers.data_ptr(), 0, 2, 2, 1, limit,
+        binding._stream(v.device)))
+    assert box.status() == 3
+    assert torch.equal(fused_out, before)
+    box.clear_status()
+    assert box.status() == 0
+    box.close()
+
     # The context still works.
     again = mgpu.segreduce(v, t, op="plus", init=0)
     assert torch.equal(again, before)
@@ -255,6 +281,7 @@ def stall_worker(rank, world, port, queue):
             torch.cuda.synchronize()
             report[step] = (box.status(),
                             None if out is None else out.cpu().numpy().tolist())
+            box.clear_status()      # so that step 3 shows its own status
             dist.barrier()
         box.close()
         pieces = [None] * world
@@ -295,7 +322,8 @@ def test_a_stalled_rank_is_detected_not_waited_for(oracle):
             vals = rep[step][1][1:]
             got[first:first + len(vals)] = vals
         assert np.array_equal(got, want)
-    assert rep0[1][0] == 0
+    assert rep0[1][0] == 0 and rep1[1][0] == 0
+    assert rep0[3][0] == 0 and rep1[3][0] == 0    # one stall, one report
     # Step 2 on rank 0: timed out waiting for rank 1's record, said so, and
     # kept the reduction of its own items in the straddling segment.
     assert rep0[2][0] == 3

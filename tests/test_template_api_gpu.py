@@ -57,3 +57,18 @@ def test_template_entry_points():
     assert "FAIL" not in run.stdout, run.stdout
     assert "ALL PASSED" in run.stdout, run.stdout + run.stderr
     assert run.returncode == 0
+
+
+def test_sharded_segreduce_program():
+    """tests/cpp/test_sharded.cu: mgpu::sharded_segreduce, the C++ entry of the
+    multi-GPU layer -- one global table of 64-bit segment starts cut into
+    shard-local tables on the devices, two shards on every GPU of the machine
+    (up to four; one GPU runs the same chain of boundary records through its
+    own mailbox), 70 steps per case, the assembled outputs against the host
+    loop of tests/test_segreduce.cu:40-49 over the whole array."""
+    run = run_program(os.path.join(ROOT, "tests", "cpp", "build",
+                                   "test_sharded"))
+    print(run.stdout)
+    assert "FAIL" not in run.stdout, run.stdout
+    assert "ALL PASSED" in run.stdout, run.stdout + run.stderr
+    assert run.returncode == 0
