@@ -653,11 +653,12 @@ def config2_strong_leg(args, rank, world, device, steps):
     box = sharded.Mailbox() if args.exchange == "p2p" else None
     records = torch.empty(world * sharded.RECORD_BYTES, dtype=torch.uint8,
                           device=device)
-    out = [None]
+    out = [torch.empty(table.numel(), dtype=torch.float32, device=device)]
 
     def fn():
         out[0] = sharded.sharded_segreduce(values, table, op="plus", init=0.0,
-                                           mailbox=box, records=records)
+                                           mailbox=box, records=records,
+                                           out=out[0])
     ms = time_steps(fn, steps, args.warmup, world, device)
     checked, worst, ok = check_headline(values, table, out[0], rank, world,
                                         max(1, host_threads() // world))
@@ -840,16 +841,19 @@ def run_ours(args, rank, world, local_rank):
             args.exchange = "nccl"
 
     last = [out]
+    shard_out = torch.empty(table.numel(), dtype=torch.float32, device=device)
 
     def step():
         if world == 1:
             mgpu.segreduce(values, seg, op="plus", init=0.0, out=out)
         elif mailbox is not None:
             last[0] = sharded.sharded_segreduce(values, table, op="plus",
-                                                init=0.0, mailbox=mailbox)
+                                                init=0.0, mailbox=mailbox,
+                                                out=shard_out)
         else:
             last[0] = sharded.sharded_segreduce(values, table, op="plus",
-                                                init=0.0, records=records)
+                                                init=0.0, records=records,
+                                                out=shard_out)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -1009,7 +1013,7 @@ def run_ours(args, rank, world, local_rank):
         else:
             secondary += config2_strong_leg(args, rank, world, device,
                                             side_steps)
-        del values, seg, table, out, records
+        del values, seg, table, out, records, shard_out
         last[0] = None
         torch.cuda.empty_cache()
         if 8 % world == 0:

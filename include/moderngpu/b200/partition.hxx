@@ -69,8 +69,9 @@ struct is_int_array {
 // A partitioner launch can carry a few extra CTAs that do unrelated work which
 // must precede the dependent kernel anyway (the multi-GPU layer posts a
 // shard's boundary record this way instead of in a launch of its own):
-// tail_t::ctas CTAs are appended to the grid and CTA k of them runs tail(k)
-// with the partitioner's nt threads.
+// the grid's first tail_t::ctas CTAs run tail(k), k = 0 .. ctas - 1, with the
+// partitioner's nt threads (first, so that they are done long before the
+// partitioner's last CTA).
 struct no_partition_tail_t {
   enum { ctas = 0 };
   MGPU_DEVICE void operator()(int) const { }
@@ -87,19 +88,19 @@ lbs_partition_k(segments_it segments, int count, int num_segments,
   // Let a dependent kernel (the reduction) set itself up meanwhile.
   ptx::grid_launch_dependents();
   if constexpr (tail_t::ctas > 0) {
-    const int first_tail = (int)gridDim.x - (int)tail_t::ctas;
-    if((int)blockIdx.x >= first_tail) {
-      tail((int)blockIdx.x - first_tail);
+    if((int)blockIdx.x < (int)tail_t::ctas) {
+      tail((int)blockIdx.x);
       return;
     }
   }
+  const int cta = (int)blockIdx.x - (int)tail_t::ctas;
   const unsigned full = 0xffffffffu;
   const int lane = (int)(threadIdx.x & 31);
   const uint32_t total = (uint32_t)count + (uint32_t)num_segments;
-  const int64_t j0 = ((int64_t)blockIdx.x * nt + threadIdx.x) * per_thread;
+  const int64_t j0 = ((int64_t)cta * nt + threadIdx.x) * per_thread;
   const uint32_t last = (uint32_t)(num_partitions - 1);
 
-  if(clear_head && 0 == blockIdx.x)
+  if(clear_head && 0 == cta)
     for(int i = (int)threadIdx.x; i < clear_head_words; i += nt)
       clear_head[i] = 0;
 

@@ -190,15 +190,15 @@ struct tile_desc_t {
   int pad;
 };
 
-// A reduction can end with one piece of work that needs every output of the
-// call: finish_t::active makes the CTAs count themselves out, and the thread
-// that finds itself last -- every output is then written and visible to it --
-// runs finish() once (the multi-GPU layer folds the following shards'
-// boundary partials into the shard's last output this way instead of in a
-// launch of its own).
+// The thread that is about to store the call's LAST output can first pass the
+// value through finish_t (the multi-GPU layer folds the following shards'
+// boundary partials into a shard's last output this way, instead of in a
+// launch of its own): finish(value) returns what is stored. Called once per
+// launch, by one thread.
 struct no_finish_t {
   enum { active = 0 };
-  MGPU_DEVICE void operator()() const { }
+  template<typename type_t>
+  MGPU_DEVICE type_t operator()(type_t value) const { return value; }
 };
 
 template<typename type_t, typename source_t, typename segments_it,
@@ -211,7 +211,7 @@ struct segreduce_args_t {
   type_t init;
   int count, num_segments, num_tiles;
   const int* partitions;
-  uint32_t* header;       // [0] ticket counter, [1] status, [2] CTAs done
+  uint32_t* header;       // [0] ticket counter, [1] status
   void* tile_state;
   uint64_t timeout_ns;    // bound on every device-side wait
   finish_t finish;
@@ -564,18 +564,18 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         if(need_out && e.b0 <= num_segments) {
           type_t result = lead;
           if(need_left && have) result = has_lead ? op(carry, lead) : carry;
+          if constexpr (finish_t::active)
+            if(e.b0 == num_segments) result = args.finish(result);
           args.output[e.b0 - 1] = result;
         }
-      }
-    }
-    if constexpr (finish_t::active) {
-      // This warp's outputs, then its count; the consumers count separately.
-      __threadfence();
-      __syncwarp();
-      if(0 == lane &&
-        2 * gridDim.x - 1 == atomicAdd(args.header + 2, 1u)) {
-        __threadfence();
-        args.finish();
+        if constexpr (finish_t::active) {
+          // The last segment starts inside the last tile: its value is the
+          // tile's last run (or `init` when a start sits on the array's end),
+          // passed through the finish step here, off the consumers' path.
+          if(e.tile == num_tiles - 1 && e.nb > 0 && num_segments > 0)
+            args.output[num_segments - 1] =
+              args.finish(e.closed ? init : tail);
+        }
       }
     }
     return;
@@ -947,6 +947,8 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     // starts than threads) the stage is released before the global stores.
     auto lookup_output = [&](auto start_of, int j, type_t& value) -> bool {
       if(0 == j) return false;
+      // With a finish step the call's last output is the carry warp's.
+      if(finish_t::active && j == num_segments) return false;
       int p = start_of(j);
       if(start_of(j - 1) == p) { value = init; return true; }
       if(j == b0) return false;          // the carry warp writes this one
@@ -1014,15 +1016,6 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
       if(edge_thread_a == tid) fixed.edge[r].tile = -1;
       ptx::mbar_arrive(&fixed.edge_full[r]);
-    }
-  }
-  if constexpr (finish_t::active) {
-    // Every consumer's outputs, then one count for all of them.
-    __threadfence();
-    ptx::named_sync<1, nt>();
-    if(0 == tid && 2 * gridDim.x - 1 == atomicAdd(args.header + 2, 1u)) {
-      __threadfence();
-      args.finish();
     }
   }
 }

@@ -23,9 +23,9 @@
 //    this or an earlier shard -- peer-to-peer stores over NVLink, three
 //    8-byte words that each carry the step number, so the reader needs no
 //    fence;
-//  * the reduction kernel's last CTA to finish reads, in ITS OWN GPU's
-//    memory, the records of the following shards and folds them into the
-//    shard's last output, in shard order.
+//  * the thread of the reduction kernel that stores the shard's last output
+//    first reads, in ITS OWN GPU's memory, the records of the following
+//    shards and folds them into that value, in shard order.
 // No collective, no extra launch, no kernel that polls another GPU's memory;
 // every wait is bounded and reports through the mailbox's status word.
 #pragma once
@@ -293,38 +293,37 @@ struct shard_post_tail_t {
   }
 };
 
-// The collect, as the last act of the shard's reduction (one thread): the
+// The collect, inside the shard's reduction: the thread that is about to
+// store the shard's last output passes the value through here first. The
 // partials of the following shards belong to the segment that is open at
 // this shard's right edge, up to and including the first shard that holds a
-// segment start of its own. The records are read from THIS GPU's mailbox as
-// they arrive; a record that does not arrive in time leaves the output
-// untouched and sets the mailbox's status word.
+// segment start of its own. The records are read from THIS GPU's mailbox
+// (they were posted before the following shards' reductions even began, so
+// they have normally long arrived); a record that does not arrive in time
+// leaves the value as it is and sets the mailbox's status word.
 template<typename type_t, typename op_t>
 struct shard_collect_finish_t {
   enum { active = 1 };
   char* mailbox;
   shard_chain_t chain;
   op_t op;
-  type_t* out;
-  int num_starts;
-  type_t init;
 
-  MGPU_DEVICE void operator()() const {
+  MGPU_DEVICE type_t operator()(type_t current) const {
     mailbox_t box = { mailbox };
     shard_record_t r;
     if(!mailbox_wait_record(box, chain.shard, chain.step, chain.timeout_ns,
       r)) {
       atomicMax(box.status(), (uint32_t)status_record_timeout);
-      return;
+      return current;
     }
     const uint32_t mine = r.flags;
-    if(!(mine & shard_has_start)) return;      // owns nothing
+    if(!(mine & shard_has_start)) return current;      // owns nothing
     bool have = false;
-    type_t acc = init;
+    type_t acc = current;
     for(int k = chain.shard + 1; k < chain.num_shards; ++k) {
       if(!mailbox_wait_record(box, k, chain.step, chain.timeout_ns, r)) {
         atomicMax(box.status(), (uint32_t)status_record_timeout);
-        return;
+        return current;
       }
       if(r.flags & shard_has_partial) {
         type_t x;
@@ -334,12 +333,8 @@ struct shard_collect_finish_t {
       }
       if(r.flags & shard_has_start) break;
     }
-    if(!have) return;
-    // The last output was written by some other CTA of this launch, which
-    // fenced before it counted itself out.
-    volatile type_t* last = out + (num_starts - 1);
-    type_t current = *last;
-    *last = (mine & shard_last_empty) ? acc : op(current, acc);
+    if(!have) return current;
+    return (mine & shard_last_empty) ? acc : op(current, acc);
   }
 };
 
@@ -641,8 +636,7 @@ void sharded_segreduce(const type_t* const* inputs, const shard_plan_t& plan,
         group.shards_per_device(), step, wait };
       tail_t tail = { inputs[v], plan.tables[v], num_starts, count, op, chain,
         group.mailbox_of(v) };
-      finish_t finish = { group.mailbox_of(v), chain, op, outputs[v],
-        num_starts, init };
+      finish_t finish = { group.mailbox_of(v), chain, op };
       detail::segreduce_enqueue<tuning_t>(source_t { inputs[v] }, count,
         (const int*)plan.tables[v], num_starts, outputs[v], op, init,
         workspace, group.stream_of(v), detail::default_timeout_ns, nullptr,

@@ -363,9 +363,9 @@ int mgpu_b200_shard_fold(int dtype, int op, const void* records_device,
  * items and store the boundary record into the mailboxes (as
  * mgpu_b200_shard_post), and tell the GPUs that hold later shards that this
  * shard is done with step - 1. mgpu_b200_shard_finish enqueues the reduction
- * kernel; its last CTA to finish folds the following shards' records into
- * out[num_starts - 1] (as mgpu_b200_shard_collect, same bounded wait and
- * status word). The two calls of a shard take the same arguments, stream and
+ * kernel; the thread that stores out[num_starts - 1] first folds the
+ * following shards' records into it (as mgpu_b200_shard_collect, same
+ * bounded wait and status word). The two calls of a shard take the same arguments, stream and
  * workspace (mgpu_b200_segreduce_workspace_bytes(dtype, count, num_starts)
  * bytes, 128-byte aligned, one per shard). A GPU that holds several shards
  * calls _begin for all of them, in shard order, before the first _finish: a

@@ -331,7 +331,7 @@ namespace {
 
 // The fused step (mgpu_b200_shard_begin / _finish): the shard's partitioner
 // with the post riding in its launch, and the shard's reduction with the
-// collect as its last act -- the same kernels mgpu::sharded_segreduce runs.
+// collect inside it -- the same kernels mgpu::sharded_segreduce runs.
 template<typename type_t, typename op_t>
 int fused_typed(int parts, const void* input, int count, const int* starts,
   int num_starts, void* out, const void* init_host, void* workspace,
@@ -346,7 +346,7 @@ int fused_typed(int parts, const void* input, int count, const int* starts,
   detail::shard_post_tail_t<type_t, op_t> tail = { (const type_t*)input,
     starts, num_starts, count, op_t(), chain, (char*)mailbox };
   detail::shard_collect_finish_t<type_t, op_t> finish = { (char*)mailbox,
-    chain, op_t(), (type_t*)out, num_starts, init };
+    chain, op_t() };
   try {
     detail::segreduce_enqueue<tuning_t>(
       detail::array_source_t<type_t> { (const type_t*)input }, count, starts,

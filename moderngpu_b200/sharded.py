@@ -16,9 +16,9 @@ launches per shard and step:
      memory of the GPUs that hold earlier shards -- peer-to-peer stores over
      NVLink into memory mapped with CUDA IPC;
   2. mgpu_b200_shard_finish: the reduction kernel on (items, shard-local
-     start table); its last CTA to finish waits -- in its own GPU's memory,
-     for a bounded time -- for the following shards' records and folds them
-     into the shard's last output, in shard order.
+     start table); the thread that stores the shard's last output first
+     waits -- in its own GPU's memory, for a bounded time -- for the
+     following shards' records and folds them in, in shard order.
 
 `Mailbox(fused=False)` runs the same exchange as four launches
 (mgpu_b200_shard_post, the reduction's two, mgpu_b200_shard_collect).
@@ -270,7 +270,7 @@ def lead_scratch(dev):
 
 
 def sharded_segreduce(values, table, op="plus", init=0, group=None,
-                      records=None, overlap=True, mailbox=None):
+                      records=None, overlap=True, mailbox=None, out=None):
     """Reduce this rank's shard and fold boundary partials across ranks.
 
     values: this rank's items (CUDA tensor); table: its shard-local start
@@ -282,16 +282,17 @@ def sharded_segreduce(values, table, op="plus", init=0, group=None,
         raise binding.LibraryMissing(
             "sharded_segreduce runs on CUDA tensors only (no CPU fallback)")
     if mailbox is not None:
-        return sharded_segreduce_multi([(values, table)], op=op, init=init,
-                                       mailbox=mailbox)[0]
+        return sharded_segreduce_multi(
+            [(values, table)], op=op, init=init, mailbox=mailbox,
+            outs=None if out is None else [out])[0]
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     return _sharded_cuda(values, table, op, init, group, rank, world, records,
-                         overlap)
+                         overlap, out)
 
 
 def _sharded_cuda(values, table, op, init, group, rank, world, records,
-                  overlap):
+                  overlap, out=None):
     lib = binding.load_library()
     dev = values.device
     dtype = binding._DTYPES[values.dtype]
@@ -311,7 +312,7 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records,
                 pending = dist.all_gather_into_tensor(records, mine,
                                                       group=group,
                                                       async_op=True)
-        out = binding.segreduce(values, table, op=op, init=init)
+        out = binding.segreduce(values, table, op=op, init=init, out=out)
         if not overlap:
             binding._check(lib.mgpu_b200_shard_pack(
                 dtype, out.data_ptr(), table.data_ptr(), table.numel(),
@@ -331,8 +332,8 @@ def _sharded_cuda(values, table, op, init, group, rank, world, records,
 
 def _sharded_mailbox(shards, op, init, outs, workspace, mailbox):
     """The fused step: every shard's partitioner (its launch also posts the
-    shard's boundary record), then every shard's reduction (its last CTA
-    collects the following shards' records): two launches per shard."""
+    shard's boundary record), then every shard's reduction (the thread that
+    stores the last output collects the following shards' records first): two launches per shard."""
     lib = mailbox.lib
     k = len(shards)
     if k != mailbox.per_gpu:
