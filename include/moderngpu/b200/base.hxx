@@ -120,13 +120,17 @@ struct cuda_exception_t : std::exception {
   }
 };
 
-// Raised when a kernel of this library reports a device-side status other
-// than success (bounded wait ran out, argument out of the supported range).
-struct status_exception_t : std::exception {
+// Raised when a kernel of this library reported a device-side status other
+// than success: a bounded wait ran out (status 1: a look-back, 2: a staged
+// copy), so the outputs of that call are incomplete. It is a
+// cuda_exception_t (cudaErrorLaunchTimeout), which is what callers of the
+// reference already catch.
+struct status_exception_t : cuda_exception_t {
   int status;
-  explicit status_exception_t(int s) : status(s) { }
+  explicit status_exception_t(int s) :
+    cuda_exception_t(cudaErrorLaunchTimeout), status(s) { }
   const char* what() const noexcept override {
-    return "mgpu: device-side status reported a failure";
+    return "mgpu: a kernel's bounded wait ran out (device-side status)";
   }
 };
 

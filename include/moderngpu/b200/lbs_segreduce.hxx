@@ -26,6 +26,7 @@ void lbs_segreduce(func_t f, int count, segments_it segments,
     tuning_t;
   typedef detail::lbs_source_t<func_t, pointers_t, type_t, args_t...>
     source_t;
+  detail::throw_on_device_status();
   detail::check_merged_size(count, num_segments);
   detail::segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);
   if(!plan.num_tiles) return;

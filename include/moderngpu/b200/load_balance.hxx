@@ -134,8 +134,8 @@ MGPU_DEVICE lbs_tile_t lbs_tile_segments(int tile, int count,
   for(int i = tid; i < flag_words; i += nt) shared.flags[i] = 0;
   __syncthreads();
   if constexpr (seg_bulk) {
-    if(!ptx::mbar_wait(&shared.bar, 0, timeout_ns) && status)
-      atomicMax(status, (uint32_t)status_copy_timeout);
+    if(!ptx::mbar_wait(&shared.bar, 0, timeout_ns) )
+      raise_status(status, (uint32_t)status_copy_timeout);
   }
 
   const int ob = t.ob, oe = t.oe;
@@ -394,7 +394,7 @@ lbs_fill_k(lbs_fill_args_t<kind, value_t> out, int count,
       const int r = k % ring;
       if(k >= ring &&
         !ptx::mbar_wait(&shared.empty[r], (k / ring - 1) & 1, timeout_ns)) {
-        atomicMax(status, (uint32_t)status_copy_timeout);
+        raise_status(status, (uint32_t)status_copy_timeout);
         return;
       }
       lbs_fill_desc_t d;
@@ -429,7 +429,7 @@ lbs_fill_k(lbs_fill_args_t<kind, value_t> out, int count,
     lbs_fill_desc_t d = shared.desc[r];
     ptx::mbar_arrive(&shared.empty[r]);
     if(!arrived) {
-      atomicMax(status, (uint32_t)status_copy_timeout);
+      raise_status(status, (uint32_t)status_copy_timeout);
       d.tile = -1;
     }
     t.tile = d.tile;
@@ -695,6 +695,7 @@ void transform_lbs(func_t f, int count, segments_it segments,
   int num_segments, pointers_t caching_iterators, context_t& context,
   args_t... args) {
   typedef typename detail::pick_lbs_tuning<launch_arg_t>::type tuning_t;
+  detail::throw_on_device_status();
   if(count < 0 || num_segments < 0 ||
     (int64_t)count + num_segments > (int64_t)0x7fffffff - 65536)
     throw cuda_exception_t(cudaErrorInvalidValue);
@@ -732,6 +733,7 @@ template<int kind, typename value_t, typename segments_it>
 void lbs_fill(lbs_fill_args_t<kind, value_t> out, int count,
   segments_it segments, int num_segments, context_t& context) {
   typedef lbs_fill_default_tuning tuning_t;
+  throw_on_device_status();
   if(!lbs_fill_sizes(count, num_segments)) return;
   mem_t<int> scratch(lbs_fill_scratch_ints<tuning_t>(count, num_segments),
     context);

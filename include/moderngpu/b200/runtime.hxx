@@ -25,6 +25,7 @@
 
 #include <algorithm>
 #include <memory>
+#include <mutex>
 #include <random>
 #include <string>
 #include <vector>
@@ -151,6 +152,69 @@ inline std::string stringprintf(const char* format, ...) {
 template<int unused>
 __global__ void arch_probe_k() { }
 
+#ifdef __CUDACC__
+////////////////////////////////////////////////////////////////////////////////
+// Device-side status, made visible to the host without a synchronisation.
+//
+// A kernel whose bounded wait runs out records a code in its call's scratch
+// (which the C++ entry points hand back to the context before anyone could
+// read it) AND in one word of pinned host memory per device. Every mgpu::
+// entry point looks at that word when it is called and
+// standard_context_t::synchronize() looks at it after waiting: a call that
+// failed surfaces as a status_exception_t (a cuda_exception_t, as for every
+// other error: reference src/moderngpu/types.hxx:9-16) at the next of these.
+// The word's device address lives in a variable of the translation unit's
+// own module, set on first use per device; code that never calls
+// throw_on_device_status() (the C ABI, which reports through its workspaces)
+// never allocates it.
+
+static __device__ uint32_t* device_sticky_status = nullptr;
+
+// Device side of every failure report.
+MGPU_DEVICE inline void raise_status(uint32_t* word, uint32_t code) {
+  if(word) atomicMax(word, code);
+  uint32_t* sticky = device_sticky_status;
+  if(sticky) *(volatile uint32_t*)sticky = code;
+}
+
+// The current device's word (host address), created on first use.
+static inline volatile uint32_t* sticky_status_word() {
+  enum { max_devices = 64 };
+  static std::mutex lock;
+  static uint32_t* words[max_devices] = { };
+  int device = 0;
+  throw_on_error(cudaGetDevice(&device));
+  if(device < 0 || device >= max_devices) return nullptr;
+  std::lock_guard<std::mutex> guard(lock);
+  if(!words[device]) {
+    uint32_t* host = nullptr;
+    uint32_t* mapped = nullptr;
+    throw_on_error(cudaHostAlloc((void**)&host, 64,
+      cudaHostAllocMapped | cudaHostAllocPortable));
+    *host = 0;
+    throw_on_error(cudaHostGetDevicePointer((void**)&mapped, host, 0));
+    throw_on_error(cudaMemcpyToSymbol(device_sticky_status, &mapped,
+      sizeof(mapped)));
+    words[device] = host;
+  }
+  return words[device];
+}
+
+// Throws status_exception_t if a kernel of an earlier call on this device
+// reported a failure (and forgets it). Does not wait for the device.
+static inline void throw_on_device_status() {
+  volatile uint32_t* word = sticky_status_word();
+  if(!word) return;
+  uint32_t code = *word;
+  if(code) {
+    *word = 0;
+    throw status_exception_t((int)code);
+  }
+}
+#else
+static inline void throw_on_device_status() { }
+#endif
+
 } // namespace detail
 
 // One-paragraph description of the current device, printed by
@@ -236,9 +300,11 @@ public:
     detail::throw_on_error(status);
   }
 
+  // Also the point at which a kernel's failed wait surfaces for certain.
   void synchronize() override {
     detail::throw_on_error(_stream ? cudaStreamSynchronize(_stream) :
       cudaDeviceSynchronize());
+    detail::throw_on_device_status();
   }
 
   cudaEvent_t event() override { return _event; }

@@ -286,7 +286,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
       const int s = j % stages;
       if(j >= stages) {
         if(!ptx::mbar_wait(&store_ready[s], ((j / stages) - 1) & 1, timeout_ns)) {
-          atomicMax(header + 1, (uint32_t)status_copy_timeout);
+          raise_status(header + 1, (uint32_t)status_copy_timeout);
           break;
         }
         store_stage(s);
@@ -299,7 +299,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
         for(int j2 = j - stages + 1 > 0 ? j - stages + 1 : 0; j2 < j; ++j2) {
           const int s2 = j2 % stages;
           if(!ptx::mbar_wait(&store_ready[s2], (j2 / stages) & 1, timeout_ns)) {
-            atomicMax(header + 1, (uint32_t)status_copy_timeout);
+            raise_status(header + 1, (uint32_t)status_copy_timeout);
             break;
           }
           store_stage(s2);
@@ -333,7 +333,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
     for(int k = 0; ; ++k) {
       const int s = k % stages;
       if(!ptx::mbar_wait(&agg_ready[s], (k / stages) & 1, timeout_ns)) {
-        if(!lane) atomicMax(header + 1, (uint32_t)status_copy_timeout);
+        if(!lane) raise_status(header + 1, (uint32_t)status_copy_timeout);
         return;
       }
       const int tile = tile_of[s];
@@ -443,7 +443,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
       if(0 == tid) ptx::mbar_arrive(&agg_ready[s]);     // lets the carry warp leave
     }
     if(!arrived) {
-      if(0 == tid) atomicMax(header + 1, (uint32_t)status_copy_timeout);
+      if(0 == tid) raise_status(header + 1, (uint32_t)status_copy_timeout);
       return;
     }
 
@@ -451,7 +451,7 @@ scan_stream_k(const type_t* input, int count, type_t* output, op_t op,
       // Finish tile k - 1.
       const int ps = prev_s;
       if(!ptx::mbar_wait(&carry_ready[ps], ((k - 1) / stages) & 1, timeout_ns))
-        atomicMax(header + 1, (uint32_t)status_copy_timeout);
+        raise_status(header + 1, (uint32_t)status_copy_timeout);
       type_t pre = prev_prefix;
       bool pre_have = prev_prefix_have;
       if(carry_have[ps]) {
@@ -629,6 +629,7 @@ void scan_event(input_it input, int count, output_it output, op_t op,
   typedef typename std::iterator_traits<input_it>::value_type type_t;
   typedef detail::scan_route_t<launch_arg_t, type_t, input_it, output_it>
     route_t;
+  detail::throw_on_device_status();
   mem_t<char> workspace(detail::scan_workspace_bytes<
     typename route_t::tuning_t, type_t, typename route_t::stream_tuning_t>(
       count), context);

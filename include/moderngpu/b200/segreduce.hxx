@@ -53,6 +53,7 @@ void segreduce(input_it input, int count, segments_it segments,
     tuning_t;
   typedef typename detail::source_for<input_it, type_t>::type source_t;
 
+  detail::throw_on_device_status();
   detail::check_merged_size(count, num_segments);
   detail::segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);
   if(!plan.num_tiles) return;
@@ -90,6 +91,7 @@ void spmv(matrix_it matrix, columns_it columns, vector_it vector, int count,
     std::is_same<typename std::remove_cv<col_t>::type, int>::value &&
     std::is_same<launch_arg_t, empty_t>::value;
   if constexpr (arrays) {
+    detail::throw_on_device_status();
     // Plain CSR arrays: matrix values and column indices are staged by bulk
     // copies, x is gathered through the read-only path.
     typedef typename detail::spmv_default_tuning<type_t>::type tuning_t;

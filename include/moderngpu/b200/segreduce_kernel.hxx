@@ -360,7 +360,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       int use = it / stages;
       if(use > 0 &&
         !ptx::mbar_wait(&fixed.empty[s], (use - 1) & 1, args.timeout_ns))
-        atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+        raise_status(args.header + 1, (uint32_t)status_copy_timeout);
       // The consumers wrote into this stage with ordinary stores; order those
       // (observed through the barrier) before the bulk copy's writes. Doing
       // it here rather than in every consumer keeps their pending global
@@ -526,7 +526,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       if(!ptx::mbar_wait(&fixed.edge_full[r], (n / ring) & 1,
         args.timeout_ns)) {
         // Never act on a record that was not delivered.
-        atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+        raise_status(args.header + 1, (uint32_t)status_copy_timeout);
         break;
       }
       const tile_edge_t<type_t> e = fixed.edge[r];
@@ -597,7 +597,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     constexpr bool shifting = decltype(shifting_tag)::value;
     int s = it % stages;
     if(!ptx::mbar_wait(&fixed.full[s], (it / stages) & 1, args.timeout_ns))
-      atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+      raise_status(args.header + 1, (uint32_t)status_copy_timeout);
     const tile_desc_t d = fixed.desc[s];
     if(d.tile < 0) return false;
 
@@ -913,7 +913,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         if(it >= ring &&
           !ptx::mbar_wait(&fixed.edge_free[r], (it / ring - 1) & 1,
             args.timeout_ns))
-          atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+          raise_status(args.header + 1, (uint32_t)status_copy_timeout);
       }
       if(edge_thread_a == tid) {
         const bool has_first = b0 >= 1 && b0 < jend;
@@ -988,7 +988,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   bool shifting = false;
   if constexpr (1 == src_bulk && seg_bulk && std::is_arithmetic<type_t>::value) {
     if(!ptx::mbar_wait(&fixed.full[0], 0, args.timeout_ns))
-      atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+      raise_status(args.header + 1, (uint32_t)status_copy_timeout);
     const tile_desc_t d = fixed.desc[0];
     bool aligned = d.tile >= 0 && d.b1 - d.b0 >= 64;
     if(aligned) {
@@ -1013,7 +1013,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       if(n >= ring &&
         !ptx::mbar_wait(&fixed.edge_free[r], (n / ring - 1) & 1,
           args.timeout_ns))
-        atomicMax(args.header + 1, (uint32_t)status_copy_timeout);
+        raise_status(args.header + 1, (uint32_t)status_copy_timeout);
       if(edge_thread_a == tid) fixed.edge[r].tile = -1;
       ptx::mbar_arrive(&fixed.edge_full[r]);
     }

@@ -614,6 +614,7 @@ void sharded_segreduce(const type_t* const* inputs, const shard_plan_t& plan,
   typedef detail::array_source_t<type_t> source_t;
   typedef detail::shard_post_tail_t<type_t, op_t> tail_t;
   typedef detail::shard_collect_finish_t<type_t, op_t> finish_t;
+  detail::throw_on_device_status();
   const int shards = plan.num_shards();
   if(shards != group.num_shards())
     throw cuda_exception_t(cudaErrorInvalidValue);

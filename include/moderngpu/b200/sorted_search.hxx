@@ -234,7 +234,7 @@ sorted_search_stream_k(const type_t* needles, int num_needles,
       if(k >= stages &&
         !ptx::mbar_wait(&shared.empty[s], ((k / stages) - 1) & 1, timeout_ns)) {
         // The stage was never released: give up and say so.
-        if(status) atomicMax(status, (uint32_t)status_copy_timeout);
+        raise_status(status, (uint32_t)status_copy_timeout);
         return;
       }
       const long long d0 = (long long)tile * nv;
@@ -287,7 +287,7 @@ sorted_search_stream_k(const type_t* needles, int num_needles,
     if(!ptx::named_all<1, nt>(arrived)) {
       // A staged copy did not complete in time: the remaining bounds stay
       // unwritten and the status word tells the host.
-      if(0 == tid && status) atomicMax(status, (uint32_t)status_copy_timeout);
+      if(0 == tid) raise_status(status, (uint32_t)status_copy_timeout);
       return;
     }
 
@@ -397,6 +397,7 @@ void sorted_search(needles_it needles, int num_needles, haystack_it haystack,
   typedef typename std::iterator_traits<needles_it>::value_type key_t;
   typedef typename detail::pick_search_tuning<launch_arg_t, key_t>::type
     tuning_t;
+  detail::throw_on_device_status();
   if(num_needles < 0 || num_haystack < 0 ||
     (int64_t)num_needles + num_haystack > (int64_t)0x7fffffff - 65536)
     throw cuda_exception_t(cudaErrorInvalidValue);

@@ -232,7 +232,7 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
     }
     value = shfl_any(value, 0);
     if(tile_empty == code) {
-      if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);
+      if(!lane) raise_status(status, (uint32_t)status_lookback_timeout);
       return false;
     }
     if(tile_closed == code) return false;
@@ -262,7 +262,7 @@ MGPU_DEVICE bool lookback(const tile_state_t<type_t>& state, int tile,
       }
     }
     if(!ready) {
-      if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);
+      if(!lane) raise_status(status, (uint32_t)status_lookback_timeout);
       return false;
     }
     // Fold lanes last..0 (earliest tile first).
@@ -367,7 +367,7 @@ MGPU_DEVICE bool lookback_wide(const tile_state_t<type_t>& state, int tile,
         uint64_t now = __shfl_sync(full, ptx::global_timer_ns(), 0);
         if(!start) start = now;
         else if(now - start > timeout_ns) {
-          if(!lane) atomicMax(status, (uint32_t)status_lookback_timeout);
+          if(!lane) raise_status(status, (uint32_t)status_lookback_timeout);
           return false;
         }
       }

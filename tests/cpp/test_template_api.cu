@@ -21,6 +21,19 @@ static void report(const char* name, bool ok) {
   if(!ok) ++failures;
 }
 
+#ifndef MGPU_TEST_ON_REFERENCE
+// One warp looks back over tile-status words that nobody ever publishes: its
+// bounded wait must run out, which the library reports as a device-side
+// status. Nothing spins forever and nothing faults.
+__global__ void unpublished_lookback_k(void* state_words, int tile,
+  uint64_t timeout_ns, uint32_t* status) {
+  detail::tile_state_t<float> state;
+  state.bind(state_words, tile + 1);
+  float carry = 0;
+  detail::lookback(state, tile, plus_t<float>(), carry, timeout_ns, status);
+}
+#endif
+
 static std::vector<int> random_segments(int count, int num_segments, int seed) {
   std::mt19937 rng(seed);
   std::uniform_int_distribution<int> dist(0, count);
@@ -662,6 +675,52 @@ int main() {
     }
     report("inner_join", ok);
   }
+
+#ifndef MGPU_TEST_ON_REFERENCE
+  // 16. A kernel whose bounded wait ran out surfaces as an exception of the
+  //     reference's type (src/moderngpu/types.hxx:9-16) at the next
+  //     context.synchronize(), or at the next mgpu:: call if the caller
+  //     waited for the device some other way; after that, calls work again.
+  {
+    mem_t<char> words(40 * 128 + 256, context);
+    cudaMemsetAsync(words.data(), 0, words.size(), context.stream());
+    uint32_t* status = (uint32_t*)words.data();
+    bool thrown = false, right_kind = false;
+    unpublished_lookback_k<<<1, 32, 0, context.stream()>>>(
+      words.data() + 256, 39, 3000000ull, status);
+    try {
+      context.synchronize();
+    } catch(cuda_exception_t& e) {
+      thrown = true;
+      right_kind = cudaErrorLaunchTimeout == e.result;
+    }
+    report("failed wait throws at context.synchronize()", thrown && right_kind);
+
+    unpublished_lookback_k<<<1, 32, 0, context.stream()>>>(
+      words.data() + 256, 39, 3000000ull, status);
+    cudaStreamSynchronize(context.stream());
+    mem_t<int> out(num_segments, context);
+    std::vector<int> ones(count, 1);
+    mem_t<int> d_ones = to_mem(ones, context);
+    int status_seen = 0;
+    try {
+      segreduce(d_ones.data(), count, d_seg.data(), num_segments, out.data(),
+        plus_t<int>(), 0, context);
+    } catch(status_exception_t& e) {
+      status_seen = e.status;
+    }
+    report("failed wait throws at the next entry point", 1 == status_seen);
+
+    segreduce(d_ones.data(), count, d_seg.data(), num_segments, out.data(),
+      plus_t<int>(), 0, context);
+    context.synchronize();
+    std::vector<int> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < num_segments; ++s)
+      ok = ok && got[s] == seg_end(seg, s, count) - seg[s];
+    report("calls work again after the report", ok);
+  }
+#endif
 
   context.synchronize();
   if(failures) printf("FAILED %d\n", failures);
