@@ -46,9 +46,13 @@ METRIC = "segreduce_throughput_256M_fp32_items"
 UNIT = "Gitems/s"
 FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the reduction kernel from
-# one ncu capture of a 2^26-item case of the same workload, divided by that
-# case's algorithmic bytes; DRAM traffic grows in proportion to the units processed.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9988
+# one ncu capture of a 2^26-item case of the same workload (profiles/
+# segreduce_k_fp32_c2.md: 278.13 MB read + 4.47 MB written for 285.21 MB of
+# algorithmic bytes; part of the results is still in the L2 when the kernel
+# ends), divided by that case's algorithmic bytes; DRAM traffic grows in
+# proportion to the units processed. To be re-captured whenever the kernel's
+# memory behaviour changes.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 0.9909
 FP32_TOL = 1e-5         # |got - ref| <= tol * max(|ref|, sum |x|), ref in fp64
 FP64_TOL = 1e-12        # the same against a long double accumulation
 
@@ -322,6 +326,21 @@ def run_reference_cuda(args, rank, world):
               "oracle/_ref/libmgpu_ref.so was not built"})
         return
     torch.cuda.set_device(0)
+    if args.config == "c3":
+        # The reference's spmv on config 3 (a profiler can be pointed at it).
+        m, c, x, r = workloads.config3(seed=2, device="cuda",
+                                       rows=1 << (22 if args.small else 24))
+        y = torch.empty(r.numel(), dtype=m.dtype, device="cuda")
+        p = lambda t: ctypes.c_void_p(t.data_ptr())      # noqa: E731
+
+        def spmv_call(pooled, sync):
+            code = ref.ref_spmv_f32(p(m), p(c), p(x), m.numel(), p(r),
+                                    r.numel(), p(y), pooled, sync)
+            assert code == 0, "reference returned CUDA error %d" % code
+        timed = time_reference_cuda(spmv_call, args.steps, m.numel())
+        emit({"impl": "reference-cuda", "config": "c3", "rows": r.numel(),
+              "nnz": m.numel(), "reference_cuda": timed})
+        return
     values, seg = workloads.config2(seed=1, count=COUNT,
                                     num_segments=NUM_SEGMENTS)
     out = torch.empty(NUM_SEGMENTS, dtype=torch.float32, device="cuda")

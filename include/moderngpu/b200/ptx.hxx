@@ -226,9 +226,18 @@ __device__ __forceinline__ void st_relaxed_u64(uint64_t* p, uint64_t v) {
   asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" :: "l"(p), "l"(v)
     : "memory");
 }
-// 16-byte accesses: one transaction each on this hardware when the address
-// is 16-byte aligned, which the tile-status protocol relies on for 8-byte
-// values (value and code travel together).
+// 16-byte accesses. ASSUMPTION the tile-status protocol makes for 8-byte
+// values (value and code travel together): a 16-byte aligned .v2.u64 access
+// is performed as ONE transaction, so a reader never sees the value of one
+// store with the code of another. The PTX memory model does not promise this
+// (it treats a vector access as its scalar parts); the hardware this library
+// targets performs aligned 128-bit global accesses as single 16-byte sector
+// transactions, the same property CUB's decoupled look-back relies on for
+// 16-byte status words. tests/cpp/test_template_api.cu stresses it: tiles of
+// 504 fp64 items, segments spanning hundreds of tiles, maximum over distinct
+// values, 50 runs compared bit for bit (a torn word would surface as a wrong
+// maximum). A port to hardware without the property has to publish through
+// atom.exch.b128 / atom.cas.b128 instead.
 __device__ __forceinline__ void ld_relaxed_v2u64(const void* p, uint64_t& a,
   uint64_t& b) {
   asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];"

@@ -76,9 +76,16 @@ struct segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 26,
 template<typename type_t>
 struct segreduce_default_tuning<type_t, 16> { typedef segreduce_tuning_t<256, 5, 3, 3> type; };
 
-// spmv stages 4 more bytes per item, so its tiles are smaller.
+// spmv stages 4 more bytes per item, and what bounds it is the number of
+// gathers from x in flight, i.e. resident warps, not tile size: ncu on
+// 2^24 rows x 16 non-zeros showed 256 x 20 tiles (2 CTAs per SM) at 31 % of
+// the warp slots, 58 % of them waiting for a load, DRAM at a third of its
+// bandwidth (1.87 ms; the reference's kernel, at 96 % of the warp slots:
+// 1.62 ms). Measured on the same matrix: 256 x 20 x 2 stages, 2 CTAs: 1.86 ms;
+// 256 x 12, 3 CTAs: 1.39; 384 x 12, 2 CTAs: 1.45; 256 x 8, 4 CTAs: 1.47;
+// 256 x 12, 4 CTAs: 3.6 (the streams of so many CTAs push x out of the L2).
 template<typename type_t, int size = (int)sizeof(type_t)>
-struct spmv_default_tuning { typedef segreduce_tuning_t<256, 20, 2, 2> type; };
+struct spmv_default_tuning { typedef segreduce_tuning_t<256, 12, 2, 3> type; };
 template<typename type_t>
 struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2> type; };
 
@@ -88,7 +95,17 @@ struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2
 // CTAs hide the functor's loads and the extra barriers best. Measured on
 // 2^28 fp32 items in 2^23 segments, functor values[index] * weight[seg]:
 // 256 x 20, 2 stages, 2 CTAs per SM: 1,293 us; 128 x 20, 1 stage, 8 CTAs:
-// 802 us. fp64 (2^27 items): 954 us against 616 us.
+// 802 us. fp64 (2^27 items): 954 us against 616 us. ncu on that shape: 37
+// thread instructions per item (the plain reduction: 13), 18 warps waiting
+// on a global load per instruction issued, DRAM at a fifth of its bandwidth:
+// the functor's loads are what every phase waits for. Tried and measured no
+// better: fewer, larger CTAs (128 x 20 with 5 or 6 CTAs per SM: 0.90 -
+// 1.05 ms; 128 x 28: 0.79), larger batches of functor calls (12: 0.83 ms,
+// 20: 1.24 ms), the tile's last rounds as a predicated batch (1.2 ms: the
+// predicates end the batching), and a software pipeline that keeps the next
+// tile's values in registers while this tile is folded (2 CTAs of 256 x 20:
+// 1.2 ms). What remains is a group of warps of its own that evaluates the
+// next tile while the consumers fold this one.
 template<typename type_t, int size = (int)sizeof(type_t)>
 struct lbs_segreduce_default_tuning {
   typedef typename segreduce_default_tuning<type_t>::type type;
@@ -654,9 +671,10 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       // Batches of `batch` items per thread: all column indices first, then
       // all gathers (independent loads in flight together), then the stores.
       // The gathers go round the L1 (they never hit there) and ask the L2 to
-      // keep x. Four in flight per thread measured best (2^24 rows x 16
-      // non-zeros, random columns: 2 -> 2.00 ms, 4 -> 1.91, 10 -> 1.95,
-      // 20 -> 2.5): more only queue up in front of the L2.
+      // keep x. Three or four in flight per thread measured best (2^24 rows
+      // x 16 non-zeros, random columns, 256 x 12 tiles: 2 -> 1.44 ms,
+      // 3 -> 1.38, 4 -> 1.39, 6 -> 1.45): more only queue up in front of
+      // the L2.
       enum { batch = vt < 4 ? vt : 4 };
       for(int first = tid; first < na; first += nt * batch) {
         int c[batch];

@@ -677,6 +677,38 @@ int main() {
   }
 
 #ifndef MGPU_TEST_ON_REFERENCE
+  // 17. Stress of the look-back words of 8-byte types ({value, code} in one
+  //     16-byte access): tiny tiles (504 items), segments that span hundreds
+  //     of tiles, maximum over distinct values, 50 runs that must all equal
+  //     the host result bit for bit. A reader that saw the value of one
+  //     publication with the code of another would return a wrong maximum.
+  {
+    const int n = 3000017, ns = 40;
+    std::mt19937 rng(1234);
+    std::vector<double> values(n);
+    for(int i = 0; i < n; ++i)
+      values[i] = (double)((i * 2654435761u) % 1000003u) + 0.5 * (i % 7);
+    std::vector<int> lseg = random_segments(n, ns, 77);
+    std::vector<double> want(ns);
+    for(int s = 0; s < ns; ++s) {
+      double x = -1.0;
+      for(int i = lseg[s]; i < seg_end(lseg, s, n); ++i)
+        x = (i == lseg[s]) ? values[i] : std::max(x, values[i]);
+      want[s] = x;
+    }
+    mem_t<double> d_values = to_mem(values, context);
+    mem_t<int> d_lseg = to_mem(lseg, context);
+    mem_t<double> out(ns, context);
+    bool ok = true;
+    for(int run = 0; run < 50 && ok; ++run) {
+      segreduce<segreduce_tuning_t<128, 4, 2, 4> >(d_values.data(), n,
+        d_lseg.data(), ns, out.data(), maximum_t<double>(), -1.0, context);
+      std::vector<double> got = from_mem(out);
+      for(int s = 0; s < ns; ++s) ok = ok && got[s] == want[s];
+    }
+    report("fp64 look-back words under stress (50 runs)", ok);
+  }
+
   // 16. A kernel whose bounded wait ran out surfaces as an exception of the
   //     reference's type (src/moderngpu/types.hxx:9-16) at the next
   //     context.synchronize(), or at the next mgpu:: call if the caller
