@@ -567,6 +567,35 @@ def time_steps(fn, steps, warmup, world, device):
     return ms
 
 
+def graph_replay_ms(call, steps, device, calls_per_graph=20):
+    """A latency-bound call timed without the host's per-call cost: the call
+    (two launches on the caller's stream, nothing else) captured
+    `calls_per_graph` times in one CUDA graph, the graph replayed `steps`
+    times between CUDA events."""
+    import torch
+    workspace = torch.empty(4 << 20, dtype=torch.uint8, device=device)
+    call(workspace)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(calls_per_graph):
+            call(workspace)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return {"ms_per_step": a.elapsed_time(b) / (steps * calls_per_graph),
+            "calls_per_graph": calls_per_graph,
+            "how": "the same call captured in a CUDA graph and replayed: "
+                   "device time per call without the host's launch cost"}
+
+
 def result_row(case, ms, units, nbytes, world, peak, peak_kind, **extra):
     gbs = nbytes / (ms * 1e-3) / 1e9
     row = {"case": case, "ms_per_step": ms,
@@ -733,6 +762,9 @@ def single_gpu_legs(args, device, steps, c2_arrays):
         "config 1: int32 plus, 1,048,576 items / 10,000 segments "
         "(latency-bound)", ms, v.numel(),
         workloads.segreduce_bytes(v.numel(), s.numel(), 4), 1, peak, peak_kind,
+        cuda_graph=graph_replay_ms(
+            lambda ws: mgpu.segreduce(v, s, init=0, out=out, workspace=ws),
+            steps, device),
         reference_cuda=theirs(lambda pooled, sync: checked(
             ref.ref_segreduce_i32(p(v), v.numel(), p(s), s.numel(), p(out), 0,
                                   0, pooled, sync)), v.numel())))

@@ -195,6 +195,28 @@ def _check(code):
         raise MgpuError(code, text)
 
 
+class _NoSwitch(object):
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on(device):
+    """Context in which `device` is the current CUDA device. When it already
+    is (the usual case) nothing is switched: torch's own context manager costs
+    several microseconds per call, which a latency-bound caller notices."""
+    if not isinstance(device, torch.device):
+        device = torch.device(device)
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
+
+
 def _stream(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
@@ -242,11 +264,12 @@ def segreduce(input, segments, op="plus", init=0, out=None, workspace=None):
         if out.numel() != num_segments:
             raise ValueError("out must have one element per segment")
     dtype = _DTYPES[input.dtype]
-    need = lib.mgpu_b200_segreduce_workspace_bytes(dtype, count, num_segments)
     if workspace is None:
-        workspace = _workspace(input.device, need)
+        workspace = _workspace(input.device,
+                               lib.mgpu_b200_segreduce_workspace_bytes(
+                                   dtype, count, num_segments))
     init_c = _CTYPES[input.dtype](init)
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         _check(lib.mgpu_b200_segreduce(
             dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
             num_segments, out.data_ptr(), ctypes.byref(init_c),
@@ -276,7 +299,7 @@ def lbs_segreduce_weighted(values, segments, weights, out=None,
         dtype, count, num_segments)
     if workspace is None:
         workspace = _workspace(values.device, need)
-    with torch.cuda.device(values.device):
+    with _on(values.device):
         _check(lib.mgpu_b200_lbs_segreduce_weighted(
             dtype, values.data_ptr(), count, segments.data_ptr(),
             num_segments, weights.data_ptr(), out.data_ptr(),
@@ -300,7 +323,7 @@ def sorted_search(needles, haystack, upper=False, out=None, workspace=None):
                                                        haystack.numel())
     if workspace is None:
         workspace = _workspace(needles.device, need)
-    with torch.cuda.device(needles.device):
+    with _on(needles.device):
         _check(lib.mgpu_b200_sorted_search(
             _DTYPES[needles.dtype], 1 if upper else 0, needles.data_ptr(),
             needles.numel(), haystack.data_ptr(), haystack.numel(),
@@ -314,7 +337,7 @@ def l2_pin(array):
     from) resident in the L2: mgpu_b200_l2_pin. Undo with l2_unpin()."""
     lib = load_library()
     _require_cuda(array, "array")
-    with torch.cuda.device(array.device):
+    with _on(array.device):
         _check(lib.mgpu_b200_l2_pin(array.data_ptr(),
                                     array.numel() * array.element_size(),
                                     _stream(array.device)))
@@ -324,7 +347,7 @@ def l2_unpin(device=None):
     lib = load_library()
     if device is None:
         device = torch.device("cuda", torch.cuda.current_device())
-    with torch.cuda.device(device):
+    with _on(device):
         _check(lib.mgpu_b200_l2_unpin(_stream(device)))
 
 
@@ -344,7 +367,7 @@ def scan(input, inclusive=False, out=None, total=None, workspace=None):
     need = lib.mgpu_b200_scan_workspace_bytes(dtype, count)
     if workspace is None:
         workspace = _workspace(input.device, need)
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         _check(lib.mgpu_b200_scan(
             dtype, 1 if inclusive else 0, input.data_ptr(), count,
             out.data_ptr(), None if total is None else total.data_ptr(),
@@ -368,7 +391,7 @@ def segreduce_static(input, segments, op="plus", init=0, out=None):
         out = torch.empty(segments.numel(), dtype=input.dtype,
                           device=input.device)
     init_c = _CTYPES[input.dtype](init)
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         _check(lib.mgpu_b200_segreduce_static(
             _DTYPES[input.dtype], _OPS[op], input.data_ptr(), input.numel(),
             segments.data_ptr(), segments.numel(), out.data_ptr(),
@@ -392,7 +415,7 @@ def segreduce_profile(input, segments, op="plus", init=0, out=None,
         workspace = _workspace(input.device, need)
     init_c = _CTYPES[input.dtype](init)
     part, red = ctypes.c_float(0), ctypes.c_float(0)
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         _check(lib.mgpu_b200_segreduce_profile(
             dtype, _OPS[op], input.data_ptr(), count, segments.data_ptr(),
             num_segments, out.data_ptr(), ctypes.byref(init_c),
@@ -409,7 +432,7 @@ def workspace_status(workspace=None, device=None):
             if device is None else torch.device(device)
         workspace = _workspace(device, 0)
     status = ctypes.c_int(0)
-    with torch.cuda.device(workspace.device):
+    with _on(workspace.device):
         code = lib.mgpu_b200_workspace_status(
             workspace.data_ptr(), _stream(workspace.device),
             ctypes.byref(status))
@@ -425,7 +448,7 @@ def load_balance_partitions(count, segments, spacing):
     num_segments = segments.numel()
     n = (count + num_segments + spacing - 1) // spacing + 1
     out = torch.empty(n, dtype=torch.int32, device=segments.device)
-    with torch.cuda.device(segments.device):
+    with _on(segments.device):
         _check(lib.mgpu_b200_load_balance_partitions(
             count, segments.data_ptr(), num_segments, spacing, out.data_ptr(),
             _stream(segments.device)))
@@ -450,7 +473,7 @@ def spmv(matrix, columns, vector, row_starts, out=None, workspace=None):
     need = lib.mgpu_b200_spmv_workspace_bytes(dtype, nnz, rows)
     if workspace is None:
         workspace = _workspace(matrix.device, need)
-    with torch.cuda.device(matrix.device):
+    with _on(matrix.device):
         _check(lib.mgpu_b200_spmv(
             dtype, matrix.data_ptr(), columns.data_ptr(), vector.data_ptr(),
             nnz, row_starts.data_ptr(), rows, out.data_ptr(),
@@ -483,7 +506,7 @@ def transform_lbs(count, segments, want_ranks=True, workspace=None,
     need = lib.mgpu_b200_lbs_workspace_bytes(count, num_segments)
     if workspace is None:
         workspace = _workspace(dev, need)
-    with torch.cuda.device(dev):
+    with _on(dev):
         _check(lib.mgpu_b200_load_balance_search(
             count, segments.data_ptr(), num_segments, seg.data_ptr(),
             rank.data_ptr() if want_ranks else None,
@@ -510,7 +533,7 @@ def interval_expand(input, count, segments, out=None, workspace=None):
     need = lib.mgpu_b200_lbs_workspace_bytes(count, num_segments)
     if workspace is None:
         workspace = _workspace(input.device, need)
-    with torch.cuda.device(input.device):
+    with _on(input.device):
         _check(lib.mgpu_b200_interval_expand(
             input.element_size(), input.data_ptr(), count,
             segments.data_ptr(), num_segments, out.data_ptr(),

@@ -232,6 +232,43 @@ def test_repeatable_integer_results(mgpu):
     assert torch.equal(a, b)
 
 
+def test_calls_replay_from_a_cuda_graph(mgpu, oracle):
+    """A call only enqueues its two launches on the caller's stream (the
+    reduction as a programmatic dependent of the partitioner): no allocation,
+    no synchronisation, no host read of device memory. So a sequence of calls
+    with a caller-supplied workspace can be captured in a CUDA graph and
+    replayed, which is how a latency-bound caller takes the host's launch cost
+    off small problems. Replays see the arrays' current contents."""
+    values, seg = workloads.config1(seed=4)
+    v, s = dev(values), dev(seg)
+    ops = [("plus", 0), ("max", -5), ("min", 7)]
+    outs = [torch.empty(seg.size, dtype=torch.int32, device="cuda")
+            for _ in ops]
+    workspace = torch.empty(4 << 20, dtype=torch.uint8, device="cuda")
+    # First use sets up per-device state (function attributes, the status
+    # word): outside the capture.
+    for (op, init), out in zip(ops, outs):
+        mgpu.segreduce(v, s, op=op, init=init, out=out, workspace=workspace)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for (op, init), out in zip(ops, outs):
+            mgpu.segreduce(v, s, op=op, init=init, out=out,
+                           workspace=workspace)
+    rng = np.random.default_rng(9)
+    for _ in range(3):
+        values = rng.integers(-1000, 1000, size=values.size).astype(np.int32)
+        v.copy_(torch.from_numpy(values))
+        for out in outs:
+            out.fill_(123456)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert mgpu.workspace_status(workspace) == 0
+        for (op, init), out in zip(ops, outs):
+            want = oracle.segreduce(values, seg, op=op, init=init)
+            assert np.array_equal(out.cpu().numpy(), want), op
+
+
 def test_host_buffer_entry_point(mgpu, oracle):
     rng = np.random.default_rng(31)
     count, num_segments = 70_000_000, 2_000_000     # three chunks
