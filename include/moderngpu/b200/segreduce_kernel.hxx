@@ -118,7 +118,7 @@ struct lbs_segreduce_default_tuning {
   typedef typename segreduce_default_tuning<type_t>::type type;
 };
 template<typename type_t>
-struct lbs_segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<128, 20, 1, 8> type; };
+struct lbs_segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<128, 28, 1, 6> type; };
 template<typename type_t>
 struct lbs_segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<128, 18, 1, 5> type; };
 
@@ -160,15 +160,45 @@ struct lbs_source_t {
   pointers_t caching;
   tuple<args_t...> args;
 
+  // What the caching iterators yield for one segment. A tile keeps these in
+  // shared memory, loaded once per segment, when it has no more segments than
+  // consumer threads and the tuple is small (the reference stages them the
+  // same way, cta_load_balance.hxx:216-244); the functor's per-item gather
+  // from global memory becomes a shared-memory read.
+  typedef tuple_iterator_value_t<pointers_t> cached_t;
+  enum {
+    cached_bytes = (tuple_size<pointers_t>::value > 0 &&
+      sizeof(cached_t) <= 16 &&
+      std::is_trivially_copyable<cached_t>::value) ?
+      (int)sizeof(cached_t) : 0
+  };
+
   template<size_t... idx>
   MGPU_DEVICE type_t call(int index, int seg, int rank,
-    index_sequence<idx...>) const {
-    return (type_t)f(index, seg, rank, mgpu::load(caching, seg),
-      get<idx>(args)...);
+    const cached_t& cached, index_sequence<idx...>) const {
+    return (type_t)f(index, seg, rank, cached, get<idx>(args)...);
+  }
+  MGPU_DEVICE cached_t fetch(int seg) const {
+    return mgpu::load(caching, seg);
+  }
+  MGPU_DEVICE type_t eval_with(int index, int seg, int rank,
+    const cached_t& cached) const {
+    return call(index, seg, rank, cached,
+      make_index_sequence<sizeof...(args_t)>());
   }
   MGPU_DEVICE type_t eval(int index, int seg, int rank) const {
-    return call(index, seg, rank, make_index_sequence<sizeof...(args_t)>());
+    return eval_with(index, seg, rank, fetch(seg));
   }
+};
+
+// Bytes per consumer thread that a source wants in every stage buffer on top
+// of the values (the per-segment tuples of lbs_source_t).
+template<typename source_t, typename = void>
+struct source_slot_bytes { enum { value = 0 }; };
+template<typename source_t>
+struct source_slot_bytes<source_t,
+  typename std::enable_if<(source_t::cached_bytes >= 0)>::type> {
+  enum { value = source_t::cached_bytes };
 };
 
 // Anything with operator[]: evaluated by the consumer threads.
@@ -262,13 +292,15 @@ struct tile_edge_t {
 // Carry warps per CTA; tile k of a CTA goes to warp k % segreduce_carry_warps.
 enum { segreduce_carry_warps = 1 };
 
-template<typename tuning_t, typename type_t, int source_kind = 1>
+template<typename tuning_t, typename type_t, int source_kind = 1,
+  int slot_bytes_ = 0>
 struct segreduce_smem_t {
   enum {
     nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
     nv = tuning_t::nv, warps = nt / 32,
     flag_words = nt * vt / 32 + 2,
     elem = (int)sizeof(type_t),
+    slot_bytes = slot_bytes_,
     wide = elem > 4 ? elem : 4,
     // spmv stages one int32 column index per item on top of everything else.
     // lbs_segreduce keeps one int32 segment id per item there instead.
@@ -277,8 +309,12 @@ struct segreduce_smem_t {
     // fold): nt - 1 of them, arithmetic types only.
     pad_bytes = std::is_arithmetic<type_t>::value ?
       (nt * elem + 127) / 128 * 128 : 0,
+    // Slots at the end of the stage for lbs_source_t's per-segment tuples:
+    // 16 bytes per consumer thread.
+    slots_offset = (nv * wide + 8 * elem + 64 + cols_bytes + 15) / 16 * 16,
+    slots = nt * (slot_bytes_ <= 4 ? 4 : (slot_bytes_ <= 8 ? 2 : 1)),
     stage_bytes = pad_bytes +
-      (nv * wide + 8 * elem + 64 + cols_bytes + 127) / 128 * 128,
+      (slots_offset + slots * slot_bytes + 127) / 128 * 128,
     ring = 32
   };
   struct fixed_t {
@@ -297,6 +333,33 @@ struct segreduce_smem_t {
     total_bytes = fixed_bytes + stages * stage_bytes
   };
 };
+
+// Functor values are evaluated round by round (one item per consumer thread
+// and round), whole rounds in straight-line batches so that a thread's loads
+// are in flight together: every batch is one trip to memory for the CTA, and
+// the trips per tile are what a functor source's time follows (measured:
+// 128 x 28 tiles, usually 27 whole rounds: batches of 7 / 8 / 9 / 10 rounds,
+// i.e. 9 / 6 / 3 / 9 trips: 0.79 / 0.69 / 0.64 / 0.81 ms on 2^28 items). So
+// the batch divides vt - 1 (a tile of nt x vt merged elements with fewer
+// segment starts than threads has vt - 1 whole rounds) where 9 does, and
+// what is left over goes in batches of 4 and 2 before single rounds.
+template<int vt>
+struct functor_batch {
+  enum { value = vt < 8 ? vt : ((vt - 1) % 9 == 0 ? 9 : 8) };
+};
+template<int batch, typename run_t>
+MGPU_DEVICE void for_whole_rounds(int& round, int full_rounds, run_t run) {
+  while(round + batch <= full_rounds)
+    run(std::integral_constant<int, batch>());
+  if constexpr (batch > 4) {
+    while(round + 4 <= full_rounds)
+      run(std::integral_constant<int, 4>());
+  }
+  if constexpr (batch > 2) {
+    if(round + 2 <= full_rounds)
+      run(std::integral_constant<int, 2>());
+  }
+}
 
 // vt consecutive values from shared memory into registers.
 template<int vt, typename type_t>
@@ -323,7 +386,8 @@ __global__ void __launch_bounds__(tuning_t::nt + 32 + 32 * segreduce_carry_warps
 segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
   op_t, finish_t> args) {
 
-  typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk> layout_t;
+  typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk,
+    source_slot_bytes<source_t>::value> layout_t;
   typedef typename layout_t::fixed_t fixed_t;
   enum { nt = tuning_t::nt, vt = tuning_t::vt, stages = tuning_t::stages,
     nv = tuning_t::nv, warps = nt / 32, flag_words = layout_t::flag_words,
@@ -656,18 +720,21 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     if constexpr (0 == src_bulk) {
       // Whole rounds in batches of straight-line loads (all in flight
       // together), the ragged rest one by one.
-      enum { batch = vt < 8 ? vt : 8 };
       const int full_rounds = na / nt;
       int round = 0;
-      for(; round + batch <= full_rounds; round += batch) {
-        type_t r[batch];
+      auto run_batch = [&](auto n_tag) {
+        constexpr int n = decltype(n_tag)::value;
+        type_t r[n];
         #pragma unroll
-        for(int k = 0; k < batch; ++k)
+        for(int k = 0; k < n; ++k)
           r[k] = args.source.load(a0 + (round + k) * nt + tid);
         #pragma unroll
-        for(int k = 0; k < batch; ++k)
+        for(int k = 0; k < n; ++k)
           vals[(round + k) * nt + tid] = r[k];
-      }
+        round += n;
+      };
+      for_whole_rounds<functor_batch<vt>::value>(round, full_rounds,
+        run_batch);
       for(int i = round * nt + tid; i < na; i += nt)
         vals[i] = args.source.load(a0 + i);
     }
@@ -725,7 +792,26 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     };
     if(all_staged) mark_heads(seg_start_staged);
     else mark_heads(seg_start);
-    int* ids = reinterpret_cast<int*>(stage + d.cols_byte);
+    [[maybe_unused]] int* ids = reinterpret_cast<int*>(stage + d.cols_byte);
+    // Segments b0 - 1 .. b1 - 1 have items in this tile. Their cached tuples
+    // go to the stage's slots (one per consumer thread) when they fit; the
+    // barriers of the id pass below order these stores before the functor
+    // rounds, and their latency hides behind that pass.
+    [[maybe_unused]] const int seg_first = b0 > 0 ? b0 - 1 : 0;
+    [[maybe_unused]] bool tuples_staged = false;
+    if constexpr (3 == src_bulk && layout_t::slot_bytes > 0) {
+      typedef typename source_t::cached_t cached_t;
+      tuples_staged = b1 - seg_first <= layout_t::slots;
+      if(tuples_staged) {
+        #pragma unroll
+        for(int k = 0; k < layout_t::slots / nt; ++k) {
+          int j = k * nt + tid;
+          if(seg_first + j < b1)
+            reinterpret_cast<cached_t*>(stage + layout_t::slots_offset)[j] =
+              args.source.fetch(seg_first + j);
+        }
+      }
+    }
     if constexpr (3 == src_bulk) {
       // Among equal starts the last segment owns the items: its id is left
       // at the head position.
@@ -811,31 +897,49 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       // thread's loads are in flight together instead of one round trip after
       // the other; only the ragged last rounds, and the one tile in which an
       // item may precede the first segment, take the item-by-item path.
-      enum { batch = vt < 8 ? vt : 8 };
-      int round = 0;
-      if(b0 > 0) {
-        const int full_rounds = na / nt;
-        for(; round + batch <= full_rounds; round += batch) {
-          type_t r[batch];
+      // evaluate(index, seg): the functor's value, the segment's tuple taken
+      // from the stage's slots or gathered from global memory.
+      auto functor_rounds = [&](auto evaluate) {
+        int round = 0;
+        // n whole rounds in straight-line code.
+        auto run_batch = [&](auto n_tag) {
+          constexpr int n = decltype(n_tag)::value;
+          type_t r[n];
           #pragma unroll
-          for(int k = 0; k < batch; ++k) {
+          for(int k = 0; k < n; ++k) {
             int i = (round + k) * nt + tid;
-            int seg = ids[i];
-            int index = a0 + i;
-            r[k] = args.source.eval(index, seg, index - seg_start(seg));
+            r[k] = evaluate(a0 + i, ids[i]);
           }
           #pragma unroll
-          for(int k = 0; k < batch; ++k)
+          for(int k = 0; k < n; ++k)
             vals[(round + k) * nt + tid] = r[k];
+          round += n;
+        };
+        if(b0 > 0)
+          for_whole_rounds<functor_batch<vt>::value>(round, na / nt,
+            run_batch);
+        for(int i = round * nt + tid; i < na; i += nt) {
+          int seg = ids[i];
+          vals[i] = seg >= 0 ? evaluate(a0 + i, seg) : init;
         }
-      }
-      for(int i = round * nt + tid; i < na; i += nt) {
-        int seg = ids[i];
-        int index = a0 + i;
-        if(seg >= 0)
-          vals[i] = args.source.eval(index, seg, index - seg_start(seg));
+      };
+      if constexpr (layout_t::slot_bytes > 0) {
+        typedef typename source_t::cached_t cached_t;
+        const cached_t* by_seg = reinterpret_cast<const cached_t*>(
+          stage + layout_t::slots_offset) - seg_first;
+        if(tuples_staged)
+          functor_rounds([&](int index, int seg) {
+            return args.source.eval_with(index, seg,
+              index - seg_start(seg), by_seg[seg]);
+          });
         else
-          vals[i] = init;
+          functor_rounds([&](int index, int seg) {
+            return args.source.eval(index, seg, index - seg_start(seg));
+          });
+      } else {
+        functor_rounds([&](int index, int seg) {
+          return args.source.eval(index, seg, index - seg_start(seg));
+        });
       }
       ptx::named_sync<1, nt>();
     }
@@ -1114,7 +1218,8 @@ void segreduce_enqueue(source_t source, int count, segments_it segments,
   cudaEvent_t after_partition = nullptr, tail_t tail = tail_t(),
   finish_t finish = finish_t(), int parts = segreduce_both_parts) {
 
-  typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk> layout_t;
+  typedef segreduce_smem_t<tuning_t, type_t, source_t::bulk,
+    source_slot_bytes<source_t>::value> layout_t;
   typedef segreduce_args_t<type_t, source_t, segments_it, output_it, op_t,
     finish_t> args_t;
   segreduce_plan_t<tuning_t, type_t> plan(count, num_segments);

@@ -169,6 +169,37 @@ int main() {
     report("lbs_segreduce cached tuple + arg, max", ok);
   }
 
+  // 2b. The same with five cached arrays: a 20-byte tuple per segment is
+  //     gathered per item instead of being kept in the tile's slots.
+  {
+    std::vector<int> values(count), weights(num_segments);
+    std::mt19937 rng(8);
+    for(int& v : values) v = (int)(rng() % 200) - 100;
+    for(int& w : weights) w = (int)(rng() % 7) - 3;
+    mem_t<int> d_values = to_mem(values, context);
+    mem_t<int> d_weights = to_mem(weights, context);
+    mem_t<int> out(num_segments, context);
+    const int* vp = d_values.data();
+    const int* wp = d_weights.data();
+    lbs_segreduce([=]MGPU_DEVICE(int index, int s, int rank,
+      tuple<int, int, int, int, int> w) {
+      return vp[index] * get<0>(w) + get<1>(w) - get<2>(w) + get<3>(w) -
+        get<4>(w) + rank;
+    }, count, d_seg.data(), num_segments, make_tuple(wp, wp, wp, wp, wp),
+      out.data(), plus_t<int>(), -1, context);
+    std::vector<int> got = from_mem(out);
+    bool ok = true;
+    for(int s = 0; s < num_segments; ++s) {
+      int x = -1;
+      for(int i = seg[s]; i < seg_end(seg, s, count); ++i) {
+        int y = values[i] * weights[s] + (i - seg[s]);
+        x = (i == seg[s]) ? y : x + y;
+      }
+      ok = ok && x == got[s];
+    }
+    report("lbs_segreduce, 20-byte cached tuple, plus", ok);
+  }
+
   // 3. segreduce on a 24-byte user type with a user combine functor, a
   //    launch_params_t in the launch slot (accepted, as demo/cities.cu:218
   //    passes one) and a lambda load iterator.
