@@ -92,27 +92,28 @@ struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2
 // lbs_segreduce keeps 4 more bytes per item in shared memory as well, and its
 // consumers compute the values themselves (search + functor), so nothing but
 // the few segment starts is staged ahead: one stage buffer and many small
-// CTAs hide the functor's loads and the extra barriers best. Measured on
-// 2^28 fp32 items in 2^23 segments, functor values[index] * weight[seg]:
-// 256 x 20, 2 stages, 2 CTAs per SM: 1,293 us; 128 x 20, 1 stage, 8 CTAs:
-// 802 us. fp64 (2^27 items): 954 us against 616 us. ncu on that shape: 37
-// thread instructions per item (the plain reduction: 13), 18 warps waiting
-// on a global load per instruction issued, DRAM at a fifth of its bandwidth:
-// the functor's loads are what every phase waits for. Tried and measured no
-// better: fewer, larger CTAs (128 x 20 with 5 or 6 CTAs per SM: 0.90 -
-// 1.05 ms; 128 x 28: 0.79), larger batches of functor calls (12: 0.83 ms,
-// 20: 1.24 ms), the tile's last rounds as a predicated batch (1.2 ms: the
-// predicates end the batching), and a software pipeline that keeps the next
-// tile's values in registers while this tile is folded (2 CTAs of 256 x 20:
-// 1.2 ms), and a group of evaluator warps of its own (as many threads as
-// consumers) that searches and evaluates tile k + 1 while the consumers fold
-// tile k
-// (0.73 - 1.05 ms over six tile shapes: the search and the functor are two
-// thirds of the work, and taking the fold away from the threads that wait on
-// the loads only halves the number of threads that have loads in flight).
-// The bound is loads in flight per SM during the functor rounds; it moves
-// with occupancy, not with batch size (batches of 16/8/4/2/1 rounds so that
-// no round is evaluated alone: 0.70 - 0.71 ms).
+// CTAs hide the functor's loads and the extra barriers best. What its time
+// follows is the number of trips to memory a tile makes, i.e. how its whole
+// rounds split into straight-line batches (see functor_batch). Measured on
+// 2^28 fp32 items in 2^23 segments, functor values[index] * weight[seg]
+// (per-segment tuples in the tile's slots): 128 x 28 x 1 stage at 6 CTAs per
+// SM 0.61 ms; 128 x 20 at 8: 0.70; 192 x 28 at 4: 0.63; 256 x 28 at 3: 0.64;
+// 256 x 24 at 4: 0.74; 384 x 20 at 3: 0.71; 256 x 28 x 2 stages at 3: 1.40.
+// Segments of 16 / 100 items on average: 0.67 / 0.58 ms. fp64 (2^27 items):
+// 128 x 18 at 5: 0.54 ms; 128 x 28 at 3: 0.61; 256 x 26 x 2 stages at 2: 0.90.
+// ncu (128 x 20 at 8): 37 thread instructions per item (the plain reduction:
+// 13), 18 warps waiting on a global load per instruction issued, DRAM at a
+// fifth of its bandwidth. Tried and measured no better: two batches in
+// flight per thread (the next batch's loads issued before this batch's
+// stores: 0.63 against 0.61 ms), batches of 12 or 20 rounds at 40 registers
+// (0.83 / 1.24 ms), the tile's last rounds as a predicated batch (1.2 ms),
+// a software pipeline that keeps the next tile's values in registers while
+// this tile is folded (2 CTAs of 256 x 20: 1.2 ms), and a group of evaluator
+// warps of its own (as many threads as consumers) that searches and
+// evaluates tile k + 1 while the consumers fold tile k (0.73 - 1.05 ms over
+// six tile shapes: the search and the functor are two thirds of the work,
+// and taking the fold away from the threads that wait on the loads only
+// halves the number of threads that have loads in flight).
 template<typename type_t, int size = (int)sizeof(type_t)>
 struct lbs_segreduce_default_tuning {
   typedef typename segreduce_default_tuning<type_t>::type type;
