@@ -111,7 +111,8 @@ struct weighted_item_t {
   const type_t* values;
   MGPU_DEVICE type_t operator()(int index, int seg, int rank,
     tuple<type_t> weight) const {
-    return values[index] * get<0>(weight);
+    // Every value is read once: a streaming load (evict-first).
+    return __ldcs(values + index) * get<0>(weight);
   }
 };
 
