@@ -303,7 +303,6 @@ struct shard_post_tail_t {
 // leaves the value as it is and sets the mailbox's status word.
 template<typename type_t, typename op_t>
 struct shard_collect_finish_t {
-  enum { active = 1 };
   char* mailbox;
   shard_chain_t chain;
   op_t op;
