@@ -71,6 +71,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   if(mbar_try_wait(bar, parity)) return true;
   uint64_t start = global_timer_ns();
   while(true) {
+    // Kept rolled: unrolled, the 32 polls are ~1.7 KB of code at every wait,
+    // and the reduction's tile loop is instruction-cache-sensitive (2 us of
+    // 195 on 2^28 items).
+    #pragma unroll 1
     for(int spin = 0; spin < 32; ++spin)
       if(mbar_try_wait(bar, parity)) return true;
     if(global_timer_ns() - start > timeout_ns) return false;

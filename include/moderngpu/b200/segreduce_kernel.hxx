@@ -791,8 +791,10 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         atomicOr(&flags[w >> 5], 1u << (w & 31));
       }
     };
-    if(all_staged) mark_heads(seg_start_staged);
-    else mark_heads(seg_start);
+    auto start_any = [&](int j) -> int {
+      return all_staged ? offs_by_seg[j] : seg_start(j);
+    };
+    mark_heads(start_any);
     [[maybe_unused]] int* ids = reinterpret_cast<int*>(stage + d.cols_byte);
     // Segments b0 - 1 .. b1 - 1 have items in this tile. Their cached tuples
     // go to the stage's slots (one per consumer thread) when they fit; the
@@ -1050,8 +1052,8 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         int prev0 = 0, p0 = 0;
         type_t lead = init;
         if(has_first) {
-          prev0 = all_staged ? seg_start_staged(b0 - 1) : seg_start(b0 - 1);
-          p0 = all_staged ? seg_start_staged(b0) : seg_start(b0);
+          prev0 = start_any(b0 - 1);
+          p0 = start_any(b0);
           unsigned q0 = (unsigned)(p0 - a0);
           if(q0 > (unsigned)na) q0 = p0 < a0 ? 0u : (unsigned)na;
           if(q0 > 0) lead = vals[slot_of(lo + (int)q0 - 1)];
@@ -1066,7 +1068,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         if(na > 0) tail = vals[slot_of(hi - 1)];
         int p_last = a1 - 1;
         if(nb > 0)
-          p_last = all_staged ? seg_start_staged(b1 - 1) : seg_start(b1 - 1);
+          p_last = start_any(b1 - 1);
         e.closed = p_last == a1;
         memcpy(e.tail, &tail, sizeof(type_t));
         ptx::mbar_arrive(&fixed.edge_full[r]);
@@ -1086,21 +1088,15 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       value = vals[slot_of(lo + (int)rel - 1)];
       return true;
     };
-    {
-      int j = b0 + tid;
-      for(; j + nt < jend_lookup; j += nt) {   // rare: more starts than threads
-        type_t value;
-        bool write = all_staged ? lookup_output(seg_start_staged, j, value) :
-          lookup_output(seg_start, j, value);
-        if(write) args.output[j - 1] = value;
-      }
+    // (More than one trip only when the tile has more starts than threads.)
+    for(int j = b0 + tid; ; j += nt) {
+      const bool more = j + nt < jend_lookup;
       type_t value;
       bool write = false;
-      if(j < jend_lookup)
-        write = all_staged ? lookup_output(seg_start_staged, j, value) :
-          lookup_output(seg_start, j, value);
-      ptx::mbar_arrive(&fixed.empty[s]);
+      if(j < jend_lookup) write = lookup_output(start_any, j, value);
+      if(!more) ptx::mbar_arrive(&fixed.empty[s]);
       if(write) args.output[j - 1] = value;
+      if(!more) break;
     }
     return true;
   };
