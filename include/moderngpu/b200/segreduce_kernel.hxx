@@ -819,8 +819,8 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       // Among equal starts the last segment owns the items: its id is left
       // at the head position.
       for(int j = b0 + tid; j < b1; j += nt) {
-        int p = seg_start(j);
-        bool owner = j + 1 >= b1 || seg_start(j + 1) != p;
+        int p = start_any(j);
+        bool owner = j + 1 >= b1 || start_any(j + 1) != p;
         int w = p - a0;
         if(owner && w >= 0 && w < na) ids[w] = j;
       }
@@ -887,10 +887,27 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       for(int k = 0; k < warp; ++k) cur = max(cur, fixed.warp_head[k]);
       cur = max(cur, before);
       if(w0 < na) {
+        // The thread's vt ids in registers, then out in 16- or 8-byte stores
+        // (slots past the tile's last item take ids as well: they are never
+        // read).
+        int id[vt];
         #pragma unroll
         for(int i = 0; i < vt; ++i) {
           if((bits >> i) & 1) cur = ids[w0 + i];
-          if(w0 + i < na) ids[w0 + i] = cur;
+          id[i] = cur;
+        }
+        if constexpr (0 == vt % 4) {
+          #pragma unroll
+          for(int i = 0; i < vt; i += 4)
+            *reinterpret_cast<int4*>(ids + w0 + i) =
+              make_int4(id[i], id[i + 1], id[i + 2], id[i + 3]);
+        } else if constexpr (0 == vt % 2) {
+          #pragma unroll
+          for(int i = 0; i < vt; i += 2)
+            *reinterpret_cast<int2*>(ids + w0 + i) = make_int2(id[i], id[i + 1]);
+        } else {
+          #pragma unroll
+          for(int i = 0; i < vt; ++i) ids[w0 + i] = id[i];
         }
       }
       ptx::named_sync<1, nt>();
@@ -933,15 +950,15 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         if(tuples_staged)
           functor_rounds([&](int index, int seg) {
             return args.source.eval_with(index, seg,
-              index - seg_start(seg), by_seg[seg]);
+              index - start_any(seg), by_seg[seg]);
           });
         else
           functor_rounds([&](int index, int seg) {
-            return args.source.eval(index, seg, index - seg_start(seg));
+            return args.source.eval(index, seg, index - start_any(seg));
           });
       } else {
         functor_rounds([&](int index, int seg) {
-          return args.source.eval(index, seg, index - seg_start(seg));
+          return args.source.eval(index, seg, index - start_any(seg));
         });
       }
       ptx::named_sync<1, nt>();
