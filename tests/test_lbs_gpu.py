@@ -169,19 +169,24 @@ def test_config4_full_size_properties(mgpu):
     assert bool((ids[1:] >= ids[:-1]).all())
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float64])
 @pytest.mark.parametrize("count,num_segments", [(0, 5), (1, 1), (1000, 37), (1_000_003, 30_011),
-                                                (5_000_000, 11), (70_000, 200_000)])
-def test_lbs_segreduce_weighted_is_exact_on_small_integers(mgpu, oracle, count, num_segments):
+                                                (5_000_000, 11), (70_000, 200_000),
+                                                (3_000_000, 500_000), (2_000_000, 250_000)])
+def test_lbs_segreduce_weighted_is_exact_on_small_integers(mgpu, oracle, count, num_segments, dtype):
     """mgpu::lbs_segreduce through the C ABI (values[index] * weight cached per
     segment, plus, init 0). Small integer values and power-of-two weights keep
-    every product and partial sum exact in fp32, so the result must equal the
-    oracle's segment sums times the weights bit for bit."""
+    every product and partial sum exact, so the result must equal the oracle's
+    segment sums times the weights bit for bit. The shapes cover tiles whose
+    segments' weights all fit the stage's slots (loaded once per segment),
+    tiles with more segments than slots (gathered per item), and mixtures of
+    both around the limits of 512 (fp32) and 256 (fp64) segments per tile."""
     rng = np.random.default_rng(count + num_segments)
-    values = rng.integers(-8, 9, size=count).astype(np.float32)
+    values = rng.integers(-8, 9, size=count).astype(dtype)
     seg = np.zeros(num_segments, dtype=np.int32)
     if num_segments > 1:
         seg[1:] = np.sort(rng.integers(0, count + 1, size=num_segments - 1))
-    weights = (2.0 ** rng.integers(-2, 3, size=num_segments)).astype(np.float32)
+    weights = (2.0 ** rng.integers(-2, 3, size=num_segments)).astype(dtype)
     got = mgpu.lbs_segreduce_weighted(torch.from_numpy(values).cuda(),
                                       torch.from_numpy(seg).cuda(),
                                       torch.from_numpy(weights).cuda()).cpu().numpy()
