@@ -327,6 +327,18 @@ struct lbs_fill_tuning_t {
     nt_ * vt_ <= 8192, "unsupported tile");
 };
 typedef lbs_fill_tuning_t<256, 20, 4> lbs_fill_default_tuning;
+// Per kind of output. Measured on 2^28 items over 2^22 segments (ids only /
+// ids + ranks): 256 x 20 at 4 CTAs per SM 186.9 / 335.5 us; 256 x 28 at 3:
+// 174.9 / 334.4; 256 x 28 at 2: 175.1 / 324.5; 192 x 28 at 4: 174.4 / 337.9;
+// 384 x 20 at 2: 228.8 / 323.8; 320 x 20 at 3: 198.9 / 331.8; tile heights that
+// are a multiple of 8 lose to bank conflicts on the 16-byte stores (256 x 16
+// at 5: 286.8 / 533.5; 256 x 24 at 4: 192.8 / 346.7).
+template<int kind>
+struct lbs_fill_tuning_for { typedef lbs_fill_default_tuning type; };
+template<>
+struct lbs_fill_tuning_for<lbs_fill_ids> { typedef lbs_fill_tuning_t<256, 28, 3> type; };
+template<>
+struct lbs_fill_tuning_for<lbs_fill_ids_ranks> { typedef lbs_fill_tuning_t<256, 28, 2> type; };
 
 struct lbs_fill_desc_t { int tile, a0, a1, pad; };
 
@@ -732,7 +744,7 @@ inline bool lbs_fill_sizes(int count, int num_segments) {
 template<int kind, typename value_t, typename segments_it>
 void lbs_fill(lbs_fill_args_t<kind, value_t> out, int count,
   segments_it segments, int num_segments, context_t& context) {
-  typedef lbs_fill_default_tuning tuning_t;
+  typedef typename lbs_fill_tuning_for<kind>::type tuning_t;
   throw_on_device_status();
   if(!lbs_fill_sizes(count, num_segments)) return;
   mem_t<int> scratch(lbs_fill_scratch_ints<tuning_t>(count, num_segments),

@@ -161,7 +161,13 @@ struct expand_t {
 };
 
 typedef detail::lbs_default_tuning lbs_tuning;
-typedef detail::lbs_fill_default_tuning fill_tuning;
+// The fill tiles of interval_expand; the searches' tiles are larger.
+typedef detail::lbs_fill_tuning_for<detail::lbs_fill_values>::type fill_tuning;
+static_assert((int)fill_tuning::nv <=
+  (int)detail::lbs_fill_tuning_for<detail::lbs_fill_ids>::type::nv &&
+  (int)fill_tuning::nv <=
+  (int)detail::lbs_fill_tuning_for<detail::lbs_fill_ids_ranks>::type::nv,
+  "lbs_bytes sizes the partition table for the smallest tile");
 
 // 4- and 8-byte elements go through the fill kernel (tile output by bulk
 // copy), 1- and 2-byte elements through the generic functor path.
@@ -643,13 +649,16 @@ int mgpu_b200_load_balance_search(int count, const int* segments_device,
       detail::lbs_fill_args_t<detail::lbs_fill_ids_ranks, int> out = { };
       out.ids = seg_out_device;
       out.ranks = rank_out_device;
-      detail::lbs_fill_enqueue<fill_tuning>(out, count, segments_device,
-        num_segments, header, partitions, s, g_timeout_ns);
+      detail::lbs_fill_enqueue<
+        detail::lbs_fill_tuning_for<detail::lbs_fill_ids_ranks>::type>(out,
+        count, segments_device, num_segments, header, partitions, s,
+        g_timeout_ns);
     } else {
       detail::lbs_fill_args_t<detail::lbs_fill_ids, int> out = { };
       out.ids = seg_out_device;
-      detail::lbs_fill_enqueue<fill_tuning>(out, count, segments_device,
-        num_segments, header, partitions, s, g_timeout_ns);
+      detail::lbs_fill_enqueue<
+        detail::lbs_fill_tuning_for<detail::lbs_fill_ids>::type>(out, count,
+        segments_device, num_segments, header, partitions, s, g_timeout_ns);
     }
   } catch(cuda_exception_t& e) {
     return cuda_code(e.result);
