@@ -333,12 +333,20 @@ typedef lbs_fill_tuning_t<256, 20, 4> lbs_fill_default_tuning;
 // 384 x 20 at 2: 228.8 / 323.8; 320 x 20 at 3: 198.9 / 331.8; tile heights that
 // are a multiple of 8 lose to bank conflicts on the 16-byte stores (256 x 16
 // at 5: 286.8 / 533.5; 256 x 24 at 4: 192.8 / 346.7).
-template<int kind>
+// Expanded values (interval_expand; the per-segment values of the next tile
+// are requested ahead like its segment starts: 237.7 -> 199.4 us for 2^28
+// 4-byte values, 290.6 -> 231.6 us for 2^27 8-byte values at 256 x 20 x 4):
+// 4-byte values 256 x 20 at 2 - 4 CTAs 198.8 - 199.9 us, 256 x 28: 201.2 -
+// 201.8, 256 x 12: 292; 8-byte values 256 x 12 at 4: 179.5 us, at 3: 212.8,
+// 256 x 20: 231 - 232, 256 x 28: 263 - 264.
+template<int kind, int value_bytes = 4>
 struct lbs_fill_tuning_for { typedef lbs_fill_default_tuning type; };
+template<int value_bytes>
+struct lbs_fill_tuning_for<lbs_fill_ids, value_bytes> { typedef lbs_fill_tuning_t<256, 28, 3> type; };
+template<int value_bytes>
+struct lbs_fill_tuning_for<lbs_fill_ids_ranks, value_bytes> { typedef lbs_fill_tuning_t<256, 28, 2> type; };
 template<>
-struct lbs_fill_tuning_for<lbs_fill_ids> { typedef lbs_fill_tuning_t<256, 28, 3> type; };
-template<>
-struct lbs_fill_tuning_for<lbs_fill_ids_ranks> { typedef lbs_fill_tuning_t<256, 28, 2> type; };
+struct lbs_fill_tuning_for<lbs_fill_values, 8> { typedef lbs_fill_tuning_t<256, 12, 4> type; };
 
 struct lbs_fill_desc_t { int tile, a0, a1, pad; };
 
@@ -468,13 +476,18 @@ lbs_fill_k(lbs_fill_args_t<kind, value_t> out, int count,
   // What a thread needs from global memory for a tile: the start it scatters
   // (segment b0 + tid) and the next one, and what describes the segment that
   // is open at the tile's left edge.
-  struct wanted_t { int p, p_next, open_start; second_t open_value; };
+  struct wanted_t {
+    int p, p_next, open_start;
+    second_t open_value, head_value;
+  };
   auto request = [&](const tile_t& t, wanted_t& w) {
     const int j = t.b0 + tid;
     w.p = w.p_next = 0;
+    w.head_value = second_t();
     if(j < t.b1) {
       w.p = start_of(j);
       if(j + 1 < t.b1) w.p_next = start_of(j + 1);
+      if constexpr (lbs_fill_values == kind) w.head_value = out.values[j];
     }
     w.open_start = 0;
     w.open_value = second_t();
@@ -499,20 +512,24 @@ lbs_fill_k(lbs_fill_args_t<kind, value_t> out, int count,
     // One head bit and one id (and, for values, the segment's value) per
     // distinct start inside the tile; among equal starts the last segment
     // owns the items.
-    auto scatter = [&](int j, int p, int p_next) {
+    auto scatter = [&](int j, int p, int p_next, second_t head_value) {
       bool owner = j + 1 >= b1 || p_next != p;
       int w = p - a0;
       if(owner && w >= 0 && w < na) {
         int u = shift + w;
         shared.heads[u] = (uint16_t)(j - b0);
         if constexpr (lbs_fill_values == kind)
-          shared.head_values[u] = out.values[j];
+          shared.head_values[u] = head_value;
         atomicOr(&flags[u >> 5], 1u << (u & 31));
       }
     };
-    if(b0 + tid < b1) scatter(b0 + tid, cur_w.p, cur_w.p_next);
-    for(int j = b0 + tid + nt; j < b1; j += nt)      // rare: many starts
-      scatter(j, start_of(j), j + 1 < b1 ? start_of(j + 1) : 0);
+    if(b0 + tid < b1)
+      scatter(b0 + tid, cur_w.p, cur_w.p_next, cur_w.head_value);
+    for(int j = b0 + tid + nt; j < b1; j += nt) {    // rare: many starts
+      second_t head_value = second_t();
+      if constexpr (lbs_fill_values == kind) head_value = out.values[j];
+      scatter(j, start_of(j), j + 1 < b1 ? start_of(j + 1) : 0, head_value);
+    }
     ptx::named_sync<1, nt>();
 
     // The other flag buffer served the previous tile, which is done with it.
@@ -744,7 +761,8 @@ inline bool lbs_fill_sizes(int count, int num_segments) {
 template<int kind, typename value_t, typename segments_it>
 void lbs_fill(lbs_fill_args_t<kind, value_t> out, int count,
   segments_it segments, int num_segments, context_t& context) {
-  typedef typename lbs_fill_tuning_for<kind>::type tuning_t;
+  typedef typename lbs_fill_tuning_for<kind, (int)sizeof(value_t)>::type
+    tuning_t;
   throw_on_device_status();
   if(!lbs_fill_sizes(count, num_segments)) return;
   mem_t<int> scratch(lbs_fill_scratch_ints<tuning_t>(count, num_segments),

@@ -161,9 +161,13 @@ struct expand_t {
 };
 
 typedef detail::lbs_default_tuning lbs_tuning;
-// The fill tiles of interval_expand; the searches' tiles are larger.
-typedef detail::lbs_fill_tuning_for<detail::lbs_fill_values>::type fill_tuning;
+// The smallest fill tile (interval_expand of 8-byte values): lbs_bytes sizes
+// the partition table for it, which serves every larger tile too.
+typedef detail::lbs_fill_tuning_for<detail::lbs_fill_values, 8>::type
+  fill_tuning;
 static_assert((int)fill_tuning::nv <=
+  (int)detail::lbs_fill_tuning_for<detail::lbs_fill_values, 4>::type::nv &&
+  (int)fill_tuning::nv <=
   (int)detail::lbs_fill_tuning_for<detail::lbs_fill_ids>::type::nv &&
   (int)fill_tuning::nv <=
   (int)detail::lbs_fill_tuning_for<detail::lbs_fill_ids_ranks>::type::nv,
@@ -180,8 +184,9 @@ int expand_fill(const void* input, int count, const int* segments,
   out.values = (const elem_t*)input;
   out.expanded = (elem_t*)output;
   try {
-    detail::lbs_fill_enqueue<fill_tuning>(out, count, segments, num_segments,
-      (uint32_t*)workspace, partitions, stream, g_timeout_ns);
+    detail::lbs_fill_enqueue<typename detail::lbs_fill_tuning_for<
+      detail::lbs_fill_values, (int)sizeof(elem_t)>::type>(out, count, segments,
+      num_segments, (uint32_t*)workspace, partitions, stream, g_timeout_ns);
   } catch(cuda_exception_t& e) {
     return cuda_code(e.result);
   }
