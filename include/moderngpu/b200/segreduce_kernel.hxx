@@ -96,11 +96,17 @@ struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2
 // follows is the number of trips to memory a tile makes, i.e. how its whole
 // rounds split into straight-line batches (see functor_batch). Measured on
 // 2^28 fp32 items in 2^23 segments, functor values[index] * weight[seg]
-// (per-segment tuples in the tile's slots): 128 x 28 x 1 stage at 6 CTAs per
-// SM 0.61 ms; 128 x 20 at 8: 0.70; 192 x 28 at 4: 0.63; 256 x 28 at 3: 0.64;
+// (per-segment tuples in the tile's slots, 32-bit segment ids per item):
+// 128 x 28 x 1 stage at 6 CTAs per SM 0.61 ms; 128 x 20 at 8: 0.70; 192 x 28 at 4: 0.63; 256 x 28 at 3: 0.64;
 // 256 x 24 at 4: 0.74; 384 x 20 at 3: 0.71; 256 x 28 x 2 stages at 3: 1.40.
 // Segments of 16 / 100 items on average: 0.67 / 0.58 ms. fp64 (2^27 items):
 // 128 x 18 at 5: 0.54 ms; 128 x 28 at 3: 0.61; 256 x 26 x 2 stages at 2: 0.90.
+// With 16-bit ids per item (relative to the segment open at the tile's left
+// edge) a CTA's shared memory drops from 34.7 to 27.7 KB and more CTAs fit:
+// 128 x 28 at 6 / 7 / 8 CTAs per SM 0.558 / 0.524 / 0.491 ms (0.561 with
+// 32-bit ids at 6); 128 x 30 at 8: 0.539; 128 x 20 at 8: 0.625; segments of
+// 12 items on average 0.749 -> 0.636 ms. fp64: 128 x 18 at 5 / 6 / 7: 0.512 /
+// 0.448 / 0.513 ms (7: spills at 40 registers); 128 x 14 at 8: 0.503.
 // ncu (128 x 20 at 8): 37 thread instructions per item (the plain reduction:
 // 13), 18 warps waiting on a global load per instruction issued, DRAM at a
 // fifth of its bandwidth. Tried and measured no better: two batches in
@@ -119,9 +125,9 @@ struct lbs_segreduce_default_tuning {
   typedef typename segreduce_default_tuning<type_t>::type type;
 };
 template<typename type_t>
-struct lbs_segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<128, 28, 1, 6> type; };
+struct lbs_segreduce_default_tuning<type_t, 4> { typedef segreduce_tuning_t<128, 28, 1, 8> type; };
 template<typename type_t>
-struct lbs_segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<128, 18, 1, 5> type; };
+struct lbs_segreduce_default_tuning<type_t, 8> { typedef segreduce_tuning_t<128, 18, 1, 6> type; };
 
 ////////////////////////////////////////////////////////////////////////////////
 // Value sources.
@@ -306,7 +312,10 @@ struct segreduce_smem_t {
     wide = elem > 4 ? elem : 4,
     // spmv stages one int32 column index per item on top of everything else.
     // lbs_segreduce keeps one int32 segment id per item there instead.
-    cols_bytes = (2 == source_kind || 3 == source_kind) ? nv * 4 + 48 : 0,
+    // (spmv: an int32 column index per item; lbs sources: a 16-bit segment id
+    // per item, relative to the segment open at the tile's left edge.)
+    cols_bytes = 2 == source_kind ? nv * 4 + 48 :
+      (3 == source_kind ? nv * 2 + 48 : 0),
     // Slots in front of the values that shifted run ends may use (see the
     // fold): nt - 1 of them, arithmetic types only.
     pad_bytes = std::is_arithmetic<type_t>::value ?
@@ -795,7 +804,11 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       return all_staged ? offs_by_seg[j] : seg_start(j);
     };
     mark_heads(start_any);
-    [[maybe_unused]] int* ids = reinterpret_cast<int*>(stage + d.cols_byte);
+    // lbs sources: ids are kept relative to segment b0 - 1, the one open at
+    // the tile's left edge (0), so that 16 bits hold them.
+    [[maybe_unused]] uint16_t* ids =
+      reinterpret_cast<uint16_t*>(stage + d.cols_byte);
+    [[maybe_unused]] const int seg_base = b0 - 1;
     // Segments b0 - 1 .. b1 - 1 have items in this tile. Their cached tuples
     // go to the stage's slots (one per consumer thread) when they fit; the
     // barriers of the id pass below order these stores before the functor
@@ -822,7 +835,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         int p = start_any(j);
         bool owner = j + 1 >= b1 || start_any(j + 1) != p;
         int w = p - a0;
-        if(owner && w >= 0 && w < na) ids[w] = j;
+        if(owner && w >= 0 && w < na) ids[w] = (uint16_t)(j - seg_base);
       }
     }
     if(0 == tid) {
@@ -872,7 +885,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         w0 & 31) & ((1u << vt) - 1);
       if(w0 >= na) bits = 0;
       else if(w0 + vt > na) bits &= (1u << (na - w0)) - 1;
-      int mine = bits ? ids[w0 + 31 - __clz(bits)] : -1;
+      int mine = bits ? (int)ids[w0 + 31 - __clz(bits)] : 0;
       int incl = mine;
       #pragma unroll
       for(int delta = 1; delta < 32; delta *= 2) {
@@ -880,34 +893,36 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
         if(lane >= delta) incl = max(incl, y);
       }
       int before = __shfl_up_sync(0xffffffffu, incl, 1);
-      if(0 == lane) before = -1;
+      if(0 == lane) before = 0;
       if(31 == lane) fixed.warp_head[warp] = incl;
       ptx::named_sync<1, nt>();
-      int cur = b0 - 1;
+      int cur = 0;
       for(int k = 0; k < warp; ++k) cur = max(cur, fixed.warp_head[k]);
       cur = max(cur, before);
       if(w0 < na) {
-        // The thread's vt ids in registers, then out in 16- or 8-byte stores
-        // (slots past the tile's last item take ids as well: they are never
-        // read).
+        // The thread's vt ids in registers, then out in 8- or 4-byte stores
+        // of four or two ids (slots past the tile's last item take ids as
+        // well: they are never read).
         int id[vt];
         #pragma unroll
         for(int i = 0; i < vt; ++i) {
-          if((bits >> i) & 1) cur = ids[w0 + i];
+          if((bits >> i) & 1) cur = (int)ids[w0 + i];
           id[i] = cur;
         }
         if constexpr (0 == vt % 4) {
           #pragma unroll
           for(int i = 0; i < vt; i += 4)
-            *reinterpret_cast<int4*>(ids + w0 + i) =
-              make_int4(id[i], id[i + 1], id[i + 2], id[i + 3]);
+            *reinterpret_cast<uint2*>(ids + w0 + i) = make_uint2(
+              (uint32_t)id[i] | ((uint32_t)id[i + 1] << 16),
+              (uint32_t)id[i + 2] | ((uint32_t)id[i + 3] << 16));
         } else if constexpr (0 == vt % 2) {
           #pragma unroll
           for(int i = 0; i < vt; i += 2)
-            *reinterpret_cast<int2*>(ids + w0 + i) = make_int2(id[i], id[i + 1]);
+            *reinterpret_cast<uint32_t*>(ids + w0 + i) =
+              (uint32_t)id[i] | ((uint32_t)id[i + 1] << 16);
         } else {
           #pragma unroll
-          for(int i = 0; i < vt; ++i) ids[w0 + i] = id[i];
+          for(int i = 0; i < vt; ++i) ids[w0 + i] = (uint16_t)id[i];
         }
       }
       ptx::named_sync<1, nt>();
@@ -928,7 +943,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           #pragma unroll
           for(int k = 0; k < n; ++k) {
             int i = (round + k) * nt + tid;
-            r[k] = evaluate(a0 + i, ids[i]);
+            r[k] = evaluate(a0 + i, seg_base + (int)ids[i]);
           }
           #pragma unroll
           for(int k = 0; k < n; ++k)
@@ -939,7 +954,7 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
           for_whole_rounds<functor_batch<vt>::value>(round, na / nt,
             run_batch);
         for(int i = round * nt + tid; i < na; i += nt) {
-          int seg = ids[i];
+          int seg = seg_base + (int)ids[i];
           vals[i] = seg >= 0 ? evaluate(a0 + i, seg) : init;
         }
       };
