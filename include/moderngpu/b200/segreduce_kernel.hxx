@@ -84,8 +84,11 @@ struct segreduce_default_tuning<type_t, 16> { typedef segreduce_tuning_t<256, 5,
 // 1.62 ms). Measured on the same matrix: 256 x 20 x 2 stages, 2 CTAs: 1.86 ms;
 // 256 x 12, 3 CTAs: 1.39; 384 x 12, 2 CTAs: 1.45; 256 x 8, 4 CTAs: 1.47;
 // 256 x 12, 4 CTAs: 3.6 (the streams of so many CTAs push x out of the L2).
+// With one stage buffer per CTA four CTAs do fit beside x: 256 x 12 x 1 stage
+// at 4 CTAs 1.363 ms against 1.388 for 2 stages at 3 (same run); at 5 or 6:
+// 2.76 - 2.79; 256 x 20 x 1 at 3 / 4: 1.47 / 1.86; 128 x 12 x 2 at 6: 1.87.
 template<typename type_t, int size = (int)sizeof(type_t)>
-struct spmv_default_tuning { typedef segreduce_tuning_t<256, 12, 2, 3> type; };
+struct spmv_default_tuning { typedef segreduce_tuning_t<256, 12, 1, 4> type; };
 template<typename type_t>
 struct spmv_default_tuning<type_t, 8> { typedef segreduce_tuning_t<256, 14, 2, 2> type; };
 
