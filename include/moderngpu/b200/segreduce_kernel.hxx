@@ -1048,21 +1048,21 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
       }
       ptx::named_sync<1, nt>();
 
-      // 4. Complete the first run end of each thread with what precedes it.
-      if(ends && !first_is_head) {
-        bool has_c = lane > 0;
-        bool head_before = 0 != (head_mask & ((1u << lane) - 1));
-        if(!head_before && warp > 0) {
-          type_t cw = warp_agg[warp - 1];
-          for(int k = warp - 1; k > 0 && !fixed.warp_head[k]; --k)
-            cw = op(warp_agg[k - 1], cw);
-          c = has_c ? op(cw, c) : cw;
-          has_c = true;
-        }
-        if(has_c) {
-          int e1 = __ffs(ends) - 1;
-          own[e1] = op(c, own[e1]);
-        }
+      // 4. Complete the first run end of each thread with what precedes it:
+      // the lanes before it in the warp (c) and, for the lanes in front of
+      // the warp's first head, what the earlier warps carry in (cw, the same
+      // for every lane: no divergence).
+      type_t cw = init;
+      if(warp > 0) {
+        cw = warp_agg[warp - 1];
+        for(int k = warp - 1; k > 0 && !fixed.warp_head[k]; --k)
+          cw = op(warp_agg[k - 1], cw);
+      }
+      const bool use_cw = warp > 0 && 0 == (head_mask & ((1u << lane) - 1));
+      if(ends && !first_is_head && (lane > 0 || use_cw)) {
+        type_t carry = lane > 0 ? (use_cw ? op(cw, c) : c) : cw;
+        int e1 = __ffs(ends) - 1;
+        own[e1] = op(carry, own[e1]);
       }
     }
 
