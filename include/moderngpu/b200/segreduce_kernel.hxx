@@ -1112,16 +1112,18 @@ segreduce_k(const segreduce_args_t<type_t, source_t, segments_it, output_it,
     // Each thread looks up at most one output per pass: the value is read
     // from the stage first, so that in the usual case (no more segment
     // starts than threads) the stage is released before the global stores.
+    // (Straight-line: the stored run end is read whether or not it is used;
+    // its slot always lies inside the stage.)
     auto lookup_output = [&](auto start_of, int j, type_t& value) -> bool {
-      if(0 == j) return false;
-      int p = start_of(j);
-      if(start_of(j - 1) == p) { value = init; return true; }
-      if(j == b0) return false;          // the carry warp writes this one
+      const int p = start_of(j);
+      const bool empty = j > 0 && start_of(j > 0 ? j - 1 : 0) == p;
       unsigned rel = (unsigned)(p - a0);
       if(rel > (unsigned)na) rel = (unsigned)na;
       if(rel < 1u) rel = 1u;
-      value = vals[slot_of(lo + (int)rel - 1)];
-      return true;
+      const type_t stored = vals[slot_of(lo + (int)rel - 1)];
+      value = empty ? init : stored;
+      // Segment b0 - 1, when it has items, is the carry warp's.
+      return j > 0 && (empty || j != b0);
     };
     // (More than one trip only when the tile has more starts than threads.)
     for(int j = b0 + tid; ; j += nt) {
